@@ -81,6 +81,7 @@ class PagedView:
     layer: int                    # index in the group
     page_tokens: int
     window: Optional[int]
+    chunk: Optional[int] = None   # a query reads only its own block of this many positions
 
 
 @dataclass
@@ -97,8 +98,15 @@ class _PagedGroup:
         self.alloc = PageAllocator(n_pages)
         # one page and one block-table row beyond what the allocators hand out: the padding rows of a decode
         # step (CacheManager.pad_slot) keep their single position there
-        self.pool = torch.zeros((n_pages + 1, len(self.entries), 2, need.kv_heads, page_tokens,
-                                 need.head_dim), dtype=dtype, device=device)
+        if need.value_dim == need.head_dim:
+            self.pool = torch.zeros((n_pages + 1, len(self.entries), 2, need.kv_heads, page_tokens,
+                                     need.head_dim), dtype=dtype, device=device)
+        else:
+            # values of another size than keys: a page-layer record is the keys [G][tokens][head_dim]
+            # followed by the values [G][tokens][v_dim] (the layout above when the two sizes agree)
+            self.pool = torch.zeros((n_pages + 1, len(self.entries),
+                                     need.kv_heads * page_tokens * (need.head_dim + need.value_dim)),
+                                    dtype=dtype, device=device)
         # pageable on purpose: a copy from pageable memory is staged by the driver before the call
         # returns, so later edits of the mirror cannot reach a copy that is still queued
         self.table_host = torch.full((n_slots + 1, width), -1, dtype=torch.int32)
@@ -110,7 +118,7 @@ class _PagedGroup:
         self.n_logical: Dict[int, int] = {}              # slot -> logical pages ever mapped
 
     def bytes_per_token(self) -> int:
-        return len(self.entries) * 2 * self.need.kv_heads * self.need.head_dim * self.pool.element_size()
+        return len(self.entries) * self.need.kv_heads * (self.need.head_dim + self.need.value_dim) * self.pool.element_size()
 
     def _mark(self, slot, lo, hi):
         d = self.dirty.get(slot)
@@ -138,10 +146,16 @@ class _PagedGroup:
 
     def trim_window(self, slot, length):
         """After `length` positions are written: pages that end at or before length-window+1
-        can no longer be read."""
-        if self.need.window is None or slot not in self.n_logical:
+        can no longer be read; with blocks of `chunk` positions, nor can pages that end at or before
+        the start of the block that position `length` (the next query) lies in."""
+        if (self.need.window is None and self.need.chunk is None) or slot not in self.n_logical:
             return
-        dead = max(0, length - self.need.window + 1) // self.page_tokens
+        first_visible = 0
+        if self.need.window is not None:
+            first_visible = max(0, length - self.need.window + 1)
+        if self.need.chunk is not None:
+            first_visible = max(first_visible, (length // self.need.chunk) * self.need.chunk)
+        dead = first_visible // self.page_tokens
         first = self.first_page.get(slot, 0)
         for i in range(first, min(dead, self.n_logical[slot])):
             self.alloc.free(int(self.table_host[slot, i]))
@@ -213,7 +227,7 @@ class CacheManager:
                 g = _PagedGroup(need, users, n_pages, self.n_slots, width, self.page_tokens, dtype, device)
                 self.paged.append(g)
                 for li, user in enumerate(users):
-                    placed[user] = PagedView(g.pool, g.table_dev, li, self.page_tokens, need.window)
+                    placed[user] = PagedView(g.pool, g.table_dev, li, self.page_tokens, need.window, need.chunk)
             else:
                 g = _StateGroup(need, users, self.n_slots, device)
                 self.fixed.append(g)
@@ -226,7 +240,7 @@ class CacheManager:
                 self._entry_view[n] = placed[(n, 0)]
         self.n_entries = len(needs)
         self._views_key, self._views = None, None
-        self.has_windows = any(g.need.window is not None for g in self.paged)
+        self.has_windows = any(g.need.window is not None or g.need.chunk is not None for g in self.paged)
         self.req_slot: Dict[object, int] = {}
         self.req_len: Dict[object, int] = {}
 
@@ -250,7 +264,7 @@ class CacheManager:
         for need in needs:
             for one in (need if isinstance(need, (list, tuple)) else [need]):
                 if isinstance(one, PagedKV):
-                    per_token += 2 * one.kv_heads * one.head_dim * element_size
+                    per_token += one.kv_heads * (one.head_dim + one.value_dim) * element_size
         if per_token == 0:
             return page_tokens
         tokens = max(min(budget // per_token, cap), page_tokens)

@@ -1,4 +1,4 @@
-"""One registry from an architecture's name (config.json `architectures[0]`) to its model.
+"""One registry from an architecture's name (config.json `architectures[0]`, or `architecture`) to its model.
 
 FeLLM's built-in path has no such table (crates/fellm-model/src/lib.rs:3-4 infers topology from
 tensor names); its plugin host keeps one (crates/fellm-plugin-host/src/registry.rs:44) and the
@@ -61,7 +61,11 @@ def read_model_config(folder):
 
 
 def config_from_dict(d: dict):
-    archs = d.get("architectures") or []
+    # `architectures` is a list whose first entry counts; a file may name its one design under
+    # `architecture` instead
+    archs = d.get("architectures") or ([d["architecture"]] if d.get("architecture") else [])
+    if isinstance(archs, str):
+        archs = [archs]
     if not archs:
         raise ConfigError("config.json: missing key 'architectures'")
     arch = get_architecture(str(archs[0]))
@@ -70,4 +74,4 @@ def config_from_dict(d: dict):
 
 def _load_builtin():
     # importing the module registers it
-    from ..models import lfm2  # noqa: F401
+    from ..models import lfm2, robazen  # noqa: F401

@@ -174,3 +174,52 @@ FELLM_API int fellm_silu_mul(const void* gu, void* out, int is_bf16, int rows, i
   if (is_bf16) return launch_k_class(launch_class_for_rows(rows, 0), silu_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, 1, (const bf16*)gu, (bf16*)out, rows, F);
   return launch_k_class(launch_class_for_rows(rows, 0), silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, 1, (const float*)gu, (float*)out, rows, F);
 }
+
+// ---------------------------------------------------------------- Dynamic Tanh norm
+// y = tanh(alpha * x) * w + b: no mean, no variance, nothing that couples the elements of a row.
+template <typename TO>
+__global__ void dyt_norm_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
+                                float alpha, TO* __restrict__ out, const int* __restrict__ rows, int n_rows, int d) {
+  pdl_launch_dependents();
+  pdl_wait();
+  size_t n = (size_t)n_rows * d;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    size_t r = i / d; int c = (int)(i - r * d);
+    size_t src = rows ? (size_t)rows[r] : r;
+    out[i] = from_f<TO>(fmaf(tanhf(alpha * x[src * d + c]), w[c], b[c]));
+  }
+}
+
+FELLM_API int fellm_dyt_norm(const float* x, const float* w, const float* b, float alpha, void* out, int out_is_bf16,
+                             const int* rows, int n_out_rows, int d, cudaStream_t stream) {
+  if (n_out_rows <= 0) return 0;
+  if (!x || !w || !b || !out) return FELLM_ERR_ARG;
+  size_t n = (size_t)n_out_rows * d;
+  int blocks = (int)((n + 255) / 256); if (blocks > fellm_sm_count() * 16) blocks = fellm_sm_count() * 16;
+  if (out_is_bf16) return launch_k_class(launch_class_for_rows(n_out_rows, 0), dyt_norm_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, 1, x, w, b, alpha, (bf16*)out, rows, n_out_rows, d);
+  return launch_k_class(launch_class_for_rows(n_out_rows, 0), dyt_norm_kernel<float>, dim3(blocks), dim3(256), 0, stream, 1, x, w, b, alpha, (float*)out, rows, n_out_rows, d);
+}
+
+// ---------------------------------------------------------------- [a | b] rows in the activation dtype
+// out[t, 0:d] = a[t, :], out[t, d:2d] = b[t, :] (float32 in): the input of a product over two streams.
+template <typename TO>
+__global__ void concat_cast_kernel(const float* __restrict__ a, const float* __restrict__ b, TO* __restrict__ out,
+                                   int rows, int d) {
+  pdl_launch_dependents();
+  pdl_wait();
+  size_t n = (size_t)rows * 2 * d;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    size_t r = i / (2 * d); int c = (int)(i - r * 2 * d);
+    out[i] = from_f<TO>(c < d ? a[r * d + c] : b[r * d + c - d]);
+  }
+}
+
+FELLM_API int fellm_concat_cast(const float* a, const float* b, void* out, int out_is_bf16, int rows, int d,
+                                cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (!a || !b || !out) return FELLM_ERR_ARG;
+  size_t n = (size_t)rows * 2 * d;
+  int blocks = (int)((n + 255) / 256); if (blocks > fellm_sm_count() * 16) blocks = fellm_sm_count() * 16;
+  if (out_is_bf16) return launch_k_class(launch_class_for_rows(rows, 0), concat_cast_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, 1, a, b, (bf16*)out, rows, d);
+  return launch_k_class(launch_class_for_rows(rows, 0), concat_cast_kernel<float>, dim3(blocks), dim3(256), 0, stream, 1, a, b, (float*)out, rows, d);
+}

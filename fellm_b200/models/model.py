@@ -63,6 +63,10 @@ def _prenorm(block, x, ctx, cache, act_dtype, reads_only):
         block.ffn.forward(h, ctx, x)
 
 
+def _with_children(part):
+    return [part] + [q for c in part.children() for q in _with_children(c)]
+
+
 class Block:
     """One layer's parts; how they are wired is looked up by the spec's arrangement name."""
 
@@ -79,7 +83,7 @@ class Block:
         self.norm_after = None
 
     def parts(self):
-        return [p for p in (self.norm1, self.mixer, self.norm2, self.ffn) if p is not None]
+        return [q for p in (self.norm1, self.mixer, self.norm2, self.ffn) if p is not None for q in _with_children(p)]
 
     def forward(self, x, ctx, cache, act_dtype, reads_only=False, norm_after=None):
         """x: float32 residual stream [T, d], updated in place."""
@@ -96,6 +100,7 @@ class Model:
         self.blocks: List[Block] = [Block(ls, dtype) for ls in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, dtype)
         self.head = build_part("head", spec.head, dtype)
+        self.connectors = [build_part("connector", cs, dtype) for cs in spec.connectors]
         self.schedule = list(spec.schedule)
 
     # ---- parameters
@@ -103,7 +108,7 @@ class Model:
         parts = [self.embedding]
         for b in self.blocks:
             parts += b.parts()
-        return parts + [self.final_norm, self.head]
+        return parts + self.connectors + [self.final_norm, self.head]
 
     def param_table(self) -> Dict[str, tuple]:
         """{tensor name in the file: (part, local name, ParamDecl)} over all parts."""
@@ -148,6 +153,8 @@ class Model:
         chain = []
         for run in self.schedule:
             b = self.blocks[run.layer]
+            if run.before is not None:
+                chain += self.connectors[run.before[0]].weight_order()
             chain += b.mixer.weight_order()
             if b.ffn is not None:
                 chain += b.ffn.weight_order()
@@ -166,8 +173,12 @@ class Model:
         head can give them without the logits it writes greedy_tokens[:wanted] and None is returned."""
         ops.forget_norm_handoff()
         x = self.embedding.forward(ctx.tokens, ctx.status)
+        # a connector reads the embedding's output again later; the blocks update x in place
+        x0 = x.clone() if self.connectors else None
         for n, run in enumerate(self.schedule):
             src = n if run.cache_of is None else run.cache_of
+            if run.before is not None:
+                x = self.connectors[run.before[0]].forward(x, x0, run.before[1], self.act_dtype)
             if n + 1 < len(self.schedule):
                 norm_after = self.blocks[self.schedule[n + 1].layer].norm1
             else:

@@ -133,6 +133,34 @@ def silu_mul(gu, out=None):
     return out
 
 
+def dyt_norm(x, w, b, alpha: float, out_dtype, rows=None, out=None):
+    """Dynamic Tanh: x float32 [T, d] -> tanh(alpha x) * w + b, [T or len(rows), d] in out_dtype."""
+    _dev(x, w, b, rows)
+    assert x.dtype == torch.float32 and w.dtype == torch.float32 and b.dtype == torch.float32 and x.is_contiguous()
+    d = x.shape[-1]
+    assert w.numel() == d and b.numel() == d
+    n = x.shape[0] if rows is None else rows.numel()
+    if rows is not None:
+        _i32(rows, "rows")
+    if out is None:
+        out = torch.empty((n, d), dtype=out_dtype, device=x.device)
+    f = _fn("elementwise", "fellm_dyt_norm", [_c_p, _c_p, _c_p, _c_f, _c_p, _c_int, _c_p, _c_int, _c_int, _c_p])
+    _check(f(_p(x), _p(w), _p(b), float(alpha), _p(out), _is_bf16(out), _p(rows), n, d, _stream()), "dyt_norm")
+    return out
+
+
+def concat_cast(a, b, out_dtype, out=None):
+    """a, b float32 [T, d] -> [T, 2d] = [a | b] in out_dtype."""
+    _dev(a, b)
+    assert a.dtype == torch.float32 and b.dtype == torch.float32 and a.is_contiguous() and b.is_contiguous() and a.shape == b.shape
+    T, d = a.shape
+    if out is None:
+        out = torch.empty((T, 2 * d), dtype=out_dtype, device=a.device)
+    f = _fn("elementwise", "fellm_concat_cast", [_c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_p(a), _p(b), _p(out), _is_bf16(out), T, d, _stream()), "concat_cast")
+    return out
+
+
 # ------------------------------------------------------------------------------ matrix products
 
 def gemm_simt(a, w, bias=None, out=None, out_dtype=None, accumulate=False):
@@ -278,6 +306,164 @@ def gemm_bf16_conv(x, w_blocked, bias, conv_w, conv_bias, state, row_slot, *, no
     return out
 
 
+# ------------------------------------------------------------------------------ recurrent mixers
+
+MAX_SCAN_KEY_DIM = 1024
+
+
+def _state_args(state):
+    assert state.dtype == torch.float32 and state[0].is_contiguous()
+    return _p(state), state.stride(0)
+
+
+def causal_conv_act(x, taps, state, item_start, item_slot, n_items, all_single, act="silu", out=None):
+    """x [T, C] (row stride free) -> act(causal conv over time per channel), taps float32 [C, L] (last column: the
+    current token); state float32 [slots, L-1, C]: the inputs before each portion, moved on by the call."""
+    _dev(x, taps, state, item_start, item_slot)
+    T, C = x.shape
+    L = taps.shape[1]
+    if not 1 <= L <= MAX_CONV_TAPS:
+        raise KernelError(f"causal_conv_act: {L} taps are outside the kernel's range 1..{MAX_CONV_TAPS}")
+    assert x.stride(1) == 1 and taps.dtype == torch.float32 and taps.is_contiguous() and taps.shape[0] == C
+    assert state.shape[1:] == (max(L - 1, 0), C) or L == 1
+    _i32(item_start, "item_start"), _i32(item_slot, "item_slot")
+    if out is None:
+        out = torch.empty((T, C), dtype=x.dtype, device=x.device)
+    sp, ss = _state_args(state)
+    f = _fn("recurrent", "fellm_causal_conv_act",
+            [_c_p, _c_int, _c_int, _c_p, _c_int, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_p(x), _is_bf16(x), x.stride(0), _p(taps), L, sp, ss, _p(item_start), _p(item_slot), _p(out), out.stride(0),
+             n_items, C, {"none": 0, "silu": 1}[act], int(all_single), _stream()), "causal_conv_act")
+    return out
+
+
+def token_shift_mix(h, mu, state, item_start, item_slot, n_items, all_single, out=None):
+    """h [T, d], mu float32 [S, d] -> [S, T, d]: h + (h_prev - h) * mu_s, h_prev the row before (the slot's state
+    float32 [slots, d] before a portion's first row; the state then takes the portion's last row)."""
+    _dev(h, mu, state, item_start, item_slot)
+    T, d = h.shape
+    S = mu.shape[0]
+    assert h.is_contiguous() and mu.dtype == torch.float32 and mu.is_contiguous() and mu.shape[1] == d
+    assert state.shape[1:] == (d,)
+    _i32(item_start, "item_start"), _i32(item_slot, "item_slot")
+    if out is None:
+        out = torch.empty((S, T, d), dtype=h.dtype, device=h.device)
+    sp, ss = _state_args(state)
+    f = _fn("recurrent", "fellm_token_shift_mix",
+            [_c_p, _c_int, _c_p, _c_int, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_p(h), _is_bf16(h), _p(mu), S, sp, ss, _p(item_start), _p(item_slot), _p(out), T, n_items, d,
+             int(all_single), _stream()), "token_shift_mix")
+    return out
+
+
+_LR_IN = {"none": 0, "tanh": 1}
+_LR_OUT = {"none": 0, "exp_neg_exp": 1, "decay_softplus": 2}
+
+
+def lowrank_expand(z, w2, bias=None, *, f_in="none", f_out="none", rate=None, per=1, out=None):
+    """out[t, n] = f_out(bias[n] + sum_r w2[n, r] f_in(z[t, r])) in float32.  z float32 [T, R] (row stride free),
+    w2 [N, R] bfloat16 or float32.  f_out 'exp_neg_exp': exp(-exp(v)); 'decay_softplus': exp(-exp(rate[n // per]) *
+    softplus(v))."""
+    _dev(z, w2, bias, rate)
+    T, R = z.shape
+    N = w2.shape[0]
+    assert z.dtype == torch.float32 and z.stride(1) == 1 and w2.is_contiguous() and w2.shape[1] == R
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == N
+    if rate is not None:
+        assert rate.dtype == torch.float32 and rate.numel() * per == N
+    if out is None:
+        out = torch.empty((T, N), dtype=torch.float32, device=z.device)
+    f = _fn("recurrent", "fellm_lowrank_expand",
+            [_c_p, _c_int, _c_p, _c_int, _c_p, _c_p, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_p(z), z.stride(0), _p(w2), _is_bf16(w2), _p(bias), _p(rate), int(per), _p(out), T, N, R, _LR_IN[f_in],
+             _LR_OUT[f_out], _stream()), "lowrank_expand")
+    return out
+
+
+def delta_scan(qkv, k_off, v_off, small, b_off, a_off, A_log, dt_bias, gch, state, item_start, item_slot, n_items,
+               H, G, dk, dv, out=None):
+    """The gated delta rule over the step's portions.  qkv [T, *]: q (G x dk) at column 0, k at k_off, v (H x dv) at
+    v_off, after convolution and SiLU; small float32 [T, *]: beta's logit at b_off + h and, for a decay per head,
+    its logit at a_off + h (A_log, dt_bias [H]); gch float32 [T, H*dk]: the decay per head and key channel itself
+    (then A_log and dt_bias are not read).  state float32 [slots, H, dk, dv].  Returns o float32 [T, H*dv]."""
+    _dev(qkv, small, A_log, dt_bias, gch, state, item_start, item_slot)
+    T = qkv.shape[0]
+    if dk > MAX_SCAN_KEY_DIM:
+        raise KernelError(f"delta_scan: key size {dk} is above the kernel's {MAX_SCAN_KEY_DIM}")
+    assert qkv.stride(1) == 1 and small.dtype == torch.float32 and small.stride(1) == 1
+    assert state.shape[1:] == (H, dk, dv)
+    if gch is not None:
+        assert gch.dtype == torch.float32 and gch.is_contiguous() and gch.shape == (T, H * dk)
+    if out is None:
+        out = torch.empty((T, H * dv), dtype=torch.float32, device=qkv.device)
+    sp, ss = _state_args(state)
+    f = _fn("recurrent", "fellm_delta_scan",
+            [_c_p, _c_int, _c_int, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_ll, _c_p, _c_p,
+             _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_p(qkv), _is_bf16(qkv), qkv.stride(0), k_off, v_off, _p(small), small.stride(0), b_off, a_off, _p(A_log),
+             _p(dt_bias), _p(gch), sp, ss, _p(item_start), _p(item_slot), _p(out), n_items, H, G, dk, dv, _stream()),
+           "delta_scan")
+    return out
+
+
+def decay_bonus_scan(r, k, v, w, u, state, item_start, item_slot, n_items, H, dk, out=None):
+    """o_t = (S + diag(u) k_t v_t^T)^T r_t; S = diag(w_t) S + k_t v_t^T per head.  r, k, v [T, H*dk] (one row stride),
+    w float32 [T, H*dk], u float32 [H, dk], state float32 [slots, H, dk, dk].  Returns o float32 [T, H*dk]."""
+    _dev(r, k, v, w, u, state, item_start, item_slot)
+    T = r.shape[0]
+    if dk > MAX_SCAN_KEY_DIM:
+        raise KernelError(f"decay_bonus_scan: key size {dk} is above the kernel's {MAX_SCAN_KEY_DIM}")
+    assert r.dtype == k.dtype == v.dtype and r.stride(0) == k.stride(0) == v.stride(0) and r.stride(1) == 1
+    assert w.dtype == torch.float32 and w.is_contiguous() and u.dtype == torch.float32 and u.is_contiguous()
+    assert state.shape[1:] == (H, dk, dk)
+    if out is None:
+        out = torch.empty((T, H * dk), dtype=torch.float32, device=r.device)
+    sp, ss = _state_args(state)
+    f = _fn("recurrent", "fellm_decay_bonus_scan",
+            [_c_p, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_p(r), _p(k), _p(v), _is_bf16(r), r.stride(0), _p(w), _p(u), sp, ss, _p(item_start), _p(item_slot), _p(out),
+             n_items, H, dk, _stream()), "decay_bonus_scan")
+    return out
+
+
+_GATE_ACT = {None: 0, "silu": 1, "sigmoid": 2}
+
+
+def head_norm_gate(o, w, per_head: bool, gate, gate_act, eps: float, H: int, dv: int, out_dtype, out=None):
+    """o float32 [T, H*dv] -> per head o / rms(o) * w * act(gate) in out_dtype.  w float32 [dv] (shared by the heads) or
+    [H*dv] (per_head); gate [T, H*dv] (row stride free), any engine dtype; gate_act 'silu' | 'sigmoid' | None."""
+    _dev(o, w, gate)
+    T = o.shape[0]
+    assert o.dtype == torch.float32 and o.is_contiguous() and w.dtype == torch.float32
+    assert w.numel() == (H * dv if per_head else dv)
+    if gate_act is not None:
+        assert gate is not None and gate.stride(1) == 1 and gate.shape == (T, H * dv)
+    if out is None:
+        out = torch.empty((T, H * dv), dtype=out_dtype, device=o.device)
+    f = _fn("recurrent", "fellm_head_norm_gate",
+            [_c_p, _c_p, _c_int, _c_p, _c_int, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_p])
+    _check(f(_p(o), _p(w), int(per_head), _p(gate), _is_bf16(gate) if gate is not None else 0,
+             gate.stride(0) if gate is not None else 0, _GATE_ACT[gate_act], _p(out), _is_bf16(out), T, H, dv, float(eps),
+             _stream()), "head_norm_gate")
+    return out
+
+
+def branch_combine(x, branches, weights, eps: float):
+    """x float32 [T, d] += mean over b of branches[b] / rms(branches[b]) * weights[b] (all float32)."""
+    _dev(x, *branches, *weights)
+    T, d = x.shape
+    n = len(branches)
+    for o, w in zip(branches, weights):
+        assert o.dtype == torch.float32 and o.is_contiguous() and o.shape == (T, d) and w.dtype == torch.float32 and w.numel() == d
+    residual_written(x)
+    arr = ctypes.c_void_p * n
+    f = _fn("recurrent", "fellm_branch_combine", [_c_p, _c_p, _c_int, _c_p, _c_int, _c_int, _c_f, _c_p])
+    _check(f(arr(*[o.data_ptr() for o in branches]), arr(*[w.data_ptr() for w in weights]), n, _p(x), T, d, float(eps),
+             _stream()), "branch_combine")
+    return x
+
+
 # ------------------------------------------------------------------------------ attention
 
 PAIRINGS = {"adjacent": 0, "split_half": 1}
@@ -339,6 +525,50 @@ def paged_attention_simt(q, pool, block_table, positions, row_slot, layer, scale
     _check(f(_p(q), _is_bf16(q), _p(pool), _is_bf16(pool), _p(block_table), block_table.shape[1],
              _p(positions), _p(row_slot), _p(out), T, H, G, hd, page_tokens, layer, pool.shape[1],
              float(scale), int(window or 0), _stream()), "paged_attention_simt")
+    return out
+
+
+def kv_write(src, k_off, v_off, pool, block_table, positions, row_slot, layer, page_tokens, G, hd, vd, status=None):
+    """The step's keys (G x hd at column k_off of src's rows) and values (G x vd at v_off) into their pages, as they
+    are.  pool [pages, layers, ...]: a page-layer record is K [G][page_tokens][hd] then V [G][page_tokens][vd]."""
+    _dev(src, pool, block_table, positions, row_slot)
+    T = src.shape[0]
+    assert src.stride(1) == 1 and pool.is_contiguous() and pool.dtype == src.dtype
+    assert pool[0, 0].numel() == G * page_tokens * (hd + vd)
+    _i32(block_table, "block_table"), _i32(positions, "positions"), _i32(row_slot, "row_slot")
+    f = _fn("attention_simt", "fellm_kv_write",
+            [_c_p, _c_int, _c_int, _c_int, _c_int, _c_p, _c_int, _c_p, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
+             _c_int, _c_int, _c_int, _c_p, _c_p])
+    _check(f(_p(src), _is_bf16(src), src.stride(0), k_off, v_off, _p(pool), _is_bf16(pool), _p(block_table),
+             block_table.shape[1], _p(positions), _p(row_slot), T, G, hd, vd, page_tokens, layer, pool.shape[1],
+             _p(status), _stream()), "kv_write")
+
+
+def paged_attention_general(q, H, hd, vd, pool, block_table, positions, row_slot, layer, page_tokens, G, scale, *,
+                            window=None, chunk=None, softcap=None, gate=None, out=None):
+    """Attention on CUDA cores with float32 arithmetic for every form the part describes: q read in place from rows
+    [T, >= H*hd] (heads at column 0), values of size vd, scores soft-capped (softcap * tanh(s / softcap)), keys limited
+    to the last `window` positions and to the query's own block of `chunk` positions, and gate float32 [T, >= H]
+    whose sigmoid scales each head's output.  Returns [T, H*vd] in q's dtype."""
+    _dev(q, pool, block_table, positions, row_slot, gate)
+    T = q.shape[0]
+    if hd > 256 or vd > 256:
+        raise KernelError(f"attention: head sizes {hd} / {vd} are above the kernel's maximum 256")
+    if H % G:
+        raise KernelError(f"attention: {H} heads are not a multiple of {G} kv heads")
+    assert q.stride(1) == 1 and pool.is_contiguous() and pool[0, 0].numel() == G * page_tokens * (hd + vd)
+    _i32(block_table, "block_table"), _i32(positions, "positions"), _i32(row_slot, "row_slot")
+    if gate is not None:
+        assert gate.dtype == torch.float32 and gate.stride(1) == 1
+    if out is None:
+        out = torch.empty((T, H * vd), dtype=q.dtype, device=q.device)
+    f = _fn("attention_simt", "fellm_paged_attention_general",
+            [_c_p, _c_int, _c_p, _c_int, _c_p, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
+             _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_f, _c_int, _c_p, _c_int, _c_p])
+    _check(f(_p(q), _is_bf16(q), _p(pool), _is_bf16(pool), _p(block_table), block_table.shape[1],
+             _p(positions), _p(row_slot), _p(out), T, H, G, hd, page_tokens, layer, pool.shape[1],
+             float(scale), int(window or 0), vd, q.stride(0), float(softcap or 0.0), int(chunk or 0), _p(gate),
+             gate.stride(0) if gate is not None else 0, _stream()), "paged_attention_general")
     return out
 
 

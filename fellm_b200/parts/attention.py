@@ -1,7 +1,14 @@
 """GQA attention mixer with optional per-head QK RMSNorm and a position encoding, over the
 paged cache (crates/fellm-model/src/graph.rs:2014-2246 for one token, 856-1050 for a batch):
 q,k,v = W xn; RMSNorm per head on q,k; rotary on q,k; k (normed, rotated) and v written to the
-cache; scores scaled by 1/sqrt(hd); kv head g = h // (H/G); causal, optionally windowed; W_o."""
+cache; scores scaled by 1/sqrt(hd); kv head g = h // (H/G); causal, optionally windowed; W_o.
+
+Beyond FeLLM's attention the part takes, as parameters: a scale of its own, a soft cap on the scores
+(cap * tanh(s / cap)), values of another size than keys (v_dim), blocks of `chunk` positions that a
+query does not look out of (counted from position 0 of the sequence), and a gate per head,
+sigmoid(W_g h), on the head's output before W_o.  Any of these sends the layer to the general
+attention kernel (CUDA cores, float32 arithmetic, both engine dtypes); without them the tensor-core
+kernels run as before."""
 from __future__ import annotations
 
 import math
@@ -17,7 +24,8 @@ from .linear import linear, linear_modules
 @register_part("mixer", "attention")
 class Attention(Mixer):
     def __init__(self, *, dtype: str, size: int, heads: int, kv_heads: int, head_dim: int, qk_norm: bool,
-                 norm_eps: float, position, window=None, shares_cache: bool = False):
+                 norm_eps: float, position, window=None, shares_cache: bool = False, scale=None, softcap=None,
+                 v_dim=None, chunk=None, head_gate: bool = False):
         """`position`: a PartSpec of the 'position' category.  `shares_cache`: this layer keeps no
         keys and values (it has no k/v weights) and reads those of the run its schedule entry
         names."""
@@ -39,11 +47,24 @@ class Attention(Mixer):
         if self.position.inv_freq is not None and self.position.inv_freq.numel() != self.rot_dim // 2:
             raise ConfigError(f"attention: the position part gives {self.position.inv_freq.numel()} frequencies "
                               f"for a rotary dimension of {self.rot_dim}")
-        self.scale = 1.0 / math.sqrt(self.hd)              # fixed in code, graph.rs:2379
+        self.scale = 1.0 / math.sqrt(self.hd) if scale is None else float(scale)      # FeLLM fixes it in code, graph.rs:2379
+        self.softcap = None if not softcap else float(softcap)
+        self.vd = self.hd if v_dim is None else int(v_dim)
+        self.chunk = None if chunk is None else int(chunk)
+        self.head_gate = bool(head_gate)
+        self.general = bool(self.softcap or self.vd != self.hd or self.chunk or self.head_gate)
+        if self.general:
+            if self.qk_norm or self.position.inv_freq is not None or self.shares_cache:
+                raise ConfigError("attention: a soft cap, v_dim, chunk or head gate goes with no QK norm, no rotation "
+                                  "and a cache of the layer's own")
+            if self.vd > 256 or self.vd < 1 or (self.chunk is not None and self.chunk < 1):
+                raise ConfigError(f"attention: v_dim {self.vd} must be in 1..256 and chunk positive")
         d, H, G, hd = self.size, self.H, self.G, self.hd
-        self.decls = {"q_proj.weight": ParamDecl((H * hd, d)), "out_proj.weight": ParamDecl((d, H * hd))}
+        self.decls = {"q_proj.weight": ParamDecl((H * hd, d)), "out_proj.weight": ParamDecl((d, H * self.vd))}
         if not self.shares_cache:
-            self.decls.update({"k_proj.weight": ParamDecl((G * hd, d)), "v_proj.weight": ParamDecl((G * hd, d))})
+            self.decls.update({"k_proj.weight": ParamDecl((G * hd, d)), "v_proj.weight": ParamDecl((G * self.vd, d))})
+        if self.head_gate:
+            self.decls["gate.weight"] = ParamDecl((H, d), init=("normal", 0.1))
         if self.qk_norm:
             self.decls["q_norm.weight"] = ParamDecl((hd,), role="vector", init=("ones",))
             if not self.shares_cache:
@@ -52,7 +73,7 @@ class Attention(Mixer):
     takes_lazy_norm = True
 
     def cache_need(self):
-        return PagedKV(self.G, self.hd, self.window)
+        return PagedKV(self.G, self.hd, self.window, self.chunk, None if self.vd == self.hd else self.vd)
 
     def prepare(self):
         q = self.w.pop("q_proj.weight")
@@ -63,16 +84,23 @@ class Attention(Mixer):
             if not (q.dtype == k.dtype == v.dtype):
                 q, k, v = q.float(), k.float(), v.float()
             self.w["qkv.weight"] = torch.cat([q, k, v], dim=0).contiguous()      # [(H+2G)*hd, d]
+        if self.general:
+            from .gated_delta import _pad_rows
+            self.w["qkv.weight"] = _pad_rows(self.w["qkv.weight"])
+            if self.head_gate:
+                self.w["gate.weight"] = _pad_rows(self.w["gate.weight"])
         self.position.to(q.device)
 
     def reserve(self, device, max_rows, n_ctx):
-        if self.w["qkv.weight"].dtype == torch.bfloat16:
+        if self.w["qkv.weight"].dtype == torch.bfloat16 and not self.general:
             floats, counters = ops.decode_scratch_need(max_rows, self.H, self.G, self.hd, n_ctx)
             ops.reserve_decode_scratch(device, 1, self.H, self.G, self.hd, 1, floats=floats, counters=counters)
 
     def forward(self, xn, ctx, cache, out, reads_only=False):
         if reads_only != self.shares_cache:
             raise ConfigError("attention: a layer built with shares_cache must run with cache_of, and only it")
+        if self.general:
+            return self._forward_general(xn, ctx, cache, out)
         G = 0 if self.shares_cache else self.G
         qkv = linear(xn, self.w["qkv.weight"])
         if (ctx.all_single and not self.shares_cache and qkv.dtype == torch.bfloat16 and self.rot_dim == self.hd
@@ -92,8 +120,24 @@ class Attention(Mixer):
         linear(a, self.w["out_proj.weight"], out=out, accumulate=True)
         return out
 
+    def _forward_general(self, xn, ctx, cache, out):
+        """q, k, v as the product leaves them: k and v into the pages, then attention over the pages with the
+        part's scale, cap, window, chunk and gate."""
+        H, G, hd, vd = self.H, self.G, self.hd, self.vd
+        gate = linear(xn, self.w["gate.weight"], out_dtype=torch.float32) if self.head_gate else None
+        qkv = linear(xn, self.w["qkv.weight"])
+        ops.kv_write(qkv, H * hd, (H + G) * hd, cache.pool, cache.block_table, ctx.positions, ctx.row_slot, cache.layer,
+                     cache.page_tokens, G, hd, vd, status=ctx.status)
+        a = ops.paged_attention_general(qkv, H, hd, vd, cache.pool, cache.block_table, ctx.positions, ctx.row_slot,
+                                        cache.layer, cache.page_tokens, G, self.scale, window=self.window,
+                                        chunk=self.chunk, softcap=self.softcap, gate=gate)
+        linear(a, self.w["out_proj.weight"], out=out, accumulate=True)
+        return out
+
     def weight_order(self):
         return [self.w["qkv.weight"], self.w["out_proj.weight"]]
 
     def kernel_modules(self, dtype):
+        if self.general:
+            return linear_modules(dtype) + [("attention_simt", None)]
         return linear_modules(dtype) + [("qk_rope_write", None)] + ops.attention_modules(dtype, self.hd)

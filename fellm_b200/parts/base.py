@@ -27,12 +27,29 @@ class ParamDecl:
     when the file stores 32-bit or the engine runs in 32-bit); 'vector': norm weights, conv taps
     and biases, always promoted to float32 (plugins/dspark/src/checkpoint.rs:154-169 promotes
     rank-1 tensors the same way); 'table': integer tables, int32.
-    `init`: ('normal', std) | ('ones',) for the random-weights mode.
-    `also`: other shapes of the same element count that a file may use."""
+    `init`: ('normal', std) | ('ones',) | ('const', value) | ('uniform', low, high) for the random-weights mode.
+    `also`: other shapes of the same element count that a file may use.
+    An extent of -1 in `shape` is read from the file (the rank of a low-rank projection, which no
+    configuration key names); `fallback` is then the shape the random-weights mode makes."""
     shape: Tuple[int, ...]
     role: str = "matrix"
     init: Tuple = ("normal", 0.02)
     also: Tuple[Tuple[int, ...], ...] = ()
+    fallback: Optional[Tuple[int, ...]] = None
+
+    def fits(self, shape) -> bool:
+        shape = tuple(shape)
+        if shape in self.also:
+            return True
+        return len(shape) == len(self.shape) and all(w == -1 or w == h for w, h in zip(self.shape, shape))
+
+    def made_shape(self) -> Tuple[int, ...]:
+        """The shape the random-weights mode gives the tensor."""
+        if -1 not in self.shape:
+            return self.shape
+        if self.fallback is None:
+            raise ValueError(f"a tensor of shape {self.shape} needs a fallback shape to be made at random")
+        return self.fallback
 
 
 # ----------------------------------------------------------------------------- cache needs
@@ -41,10 +58,19 @@ class ParamDecl:
 @dataclass(frozen=True)
 class PagedKV:
     """Keys and values per token: `kv_heads * head_dim` each.  `window` = how many of the
-    latest positions a query reads (None: all of them)."""
+    latest positions a query reads (None: all of them).  `chunk`: a query reads only keys of its
+    own block of `chunk` positions, counted from position 0 (None: no such blocks).  `v_dim`: the
+    size of a value where it differs from a key's (None: head_dim); a page-layer record is then the
+    keys [kv_heads][page_tokens][head_dim] followed by the values [kv_heads][page_tokens][v_dim]."""
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    chunk: Optional[int] = None
+    v_dim: Optional[int] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_dim is None else self.v_dim
 
 
 @dataclass(frozen=True)
@@ -89,6 +115,11 @@ class Part:
         they can be compiled before the first step."""
         return []
 
+    def children(self):
+        """Parts this part is made of that own tensors of their own (each built from a PartSpec): the
+        model binds, reserves and compiles for them as for the parts of a block."""
+        return []
+
 
 class Norm(Part):
     def forward(self, x: torch.Tensor, out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None):
@@ -129,6 +160,15 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class Connector(Part):
+    """Rewrites the residual stream between two blocks (e.g. where a looped run of layers starts a
+    pass): forward(x, x0, step) returns the new float32 [T, d] stream; x0 is the embedding's output,
+    `step` the number of the pass."""
+
+    def forward(self, x: torch.Tensor, x0: torch.Tensor, step: int, act_dtype: torch.dtype) -> torch.Tensor:
+        raise NotImplementedError
+
+
 class Embedding(Part):
     def forward(self, tokens: torch.Tensor) -> torch.Tensor:
         """tokens int32 [T] -> float32 [T, d]."""
@@ -155,9 +195,10 @@ NORMS: Dict[str, type] = {}
 POSITION_ENCODINGS: Dict[str, type] = {}
 EMBEDDINGS: Dict[str, type] = {}
 HEADS: Dict[str, type] = {}
+CONNECTORS: Dict[str, type] = {}
 
 _TABLES = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS,
-           "position": POSITION_ENCODINGS, "embedding": EMBEDDINGS, "head": HEADS}
+           "position": POSITION_ENCODINGS, "embedding": EMBEDDINGS, "head": HEADS, "connector": CONNECTORS}
 
 
 def register_part(category: str, kind: str):

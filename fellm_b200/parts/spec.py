@@ -54,9 +54,12 @@ class Run:
     """One entry of the order in which layers run.  `layer` indexes ModelSpec.layers and may
     appear in several entries (the same weights run again, with a cache of their own).
     `cache_of`, when set, is the index of an EARLIER entry whose cache this entry reads instead
-    of keeping one."""
+    of keeping one.  `before`, when set, is (index into ModelSpec.connectors, pass number): that
+    connector rewrites the residual stream right before this entry's block (the entry that opens a
+    pass of a looped run of layers)."""
     layer: int
     cache_of: Optional[int] = None
+    before: Optional[Tuple[int, int]] = None
 
 
 @dataclass
@@ -70,6 +73,7 @@ class ModelSpec:
     final_norm: PartSpec
     head: PartSpec
     schedule: List[Run] = field(default_factory=list)
+    connectors: List[PartSpec] = field(default_factory=list)
 
     def __post_init__(self):
         if not self.schedule:
@@ -77,6 +81,8 @@ class ModelSpec:
         for n, run in enumerate(self.schedule):
             if not 0 <= run.layer < len(self.layers):
                 raise ValueError(f"schedule entry {n} names layer {run.layer} of {len(self.layers)}")
+            if run.before is not None and not 0 <= run.before[0] < len(self.connectors):
+                raise ValueError(f"schedule entry {n} names connector {run.before[0]} of {len(self.connectors)}")
             if run.cache_of is not None:
                 if not 0 <= run.cache_of < n:
                     raise ValueError(f"schedule entry {n} reads the cache of entry {run.cache_of}, "

@@ -35,7 +35,10 @@ def kept_dtype(role: str, stored: torch.dtype, engine_dtype: str) -> torch.dtype
 
 def _convert(t: torch.Tensor, decl, engine_dtype: str, device) -> torch.Tensor:
     want = kept_dtype(decl.role, t.dtype, engine_dtype)
-    t = t.reshape(decl.shape)
+    shape = tuple(decl.shape)
+    if -1 in shape and len(t.shape) == len(shape):          # an extent the file decides
+        shape = tuple(h if w == -1 else w for w, h in zip(shape, t.shape))
+    t = t.reshape(shape)
     return t.to(device=device, dtype=want).contiguous()
 
 
@@ -52,7 +55,7 @@ def check_and_collect(model, available: Dict[str, tuple]):
     for name, (_, _, decl) in table.items():
         if name in available:
             shape = tuple(available[name])
-            if shape != tuple(decl.shape) and shape not in decl.also:
+            if not decl.fits(shape):
                 wrong.append(f"{name}: file has {list(shape)}, model wants {list(decl.shape)}")
     return missing, unexpected, wrong
 

@@ -30,11 +30,17 @@ def random_tensors(model, seed: int, store_dtype=torch.bfloat16) -> Dict[str, to
     out = {}
     for name, (_, _, decl) in model.param_table().items():
         if decl.init[0] == "ones":
-            t = torch.ones(decl.shape, dtype=torch.float32)
+            t = torch.ones(decl.made_shape(), dtype=torch.float32)
         elif decl.init[0] == "normal":
             g = torch.Generator(device="cpu")
             g.manual_seed(_tensor_seed(seed, name))
-            t = torch.empty(decl.shape, dtype=torch.float32).normal_(0.0, float(decl.init[1]), generator=g)
+            t = torch.empty(decl.made_shape(), dtype=torch.float32).normal_(0.0, float(decl.init[1]), generator=g)
+        elif decl.init[0] == "const":
+            t = torch.full(decl.made_shape(), float(decl.init[1]), dtype=torch.float32)
+        elif decl.init[0] == "uniform":
+            g = torch.Generator(device="cpu")
+            g.manual_seed(_tensor_seed(seed, name))
+            t = torch.empty(decl.made_shape(), dtype=torch.float32).uniform_(float(decl.init[1]), float(decl.init[2]), generator=g)
         else:
             raise ValueError(f"unknown init {decl.init!r} for {name}")
         out[name] = t.to(store_dtype)
