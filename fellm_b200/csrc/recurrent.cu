@@ -79,7 +79,7 @@ FELLM_API int fellm_causal_conv_act(const void* x, int is_bf16, int ldx, const f
                                     int ldo, int n_items, int C, int act, int all_single, cudaStream_t stream) {
   if (n_items <= 0 || C <= 0) return 0;
   if (L < 1 || L > MAX_TAPS) return FELLM_ERR_SIZE;
-  if (!x || !taps || !state || !item_start || !item_slot || !out) return FELLM_ERR_ARG;
+  if (!x || !taps || (!state && L > 1) || !item_start || !item_slot || !out) return FELLM_ERR_ARG;
   dim3 grid(ceil_div(C, CH_TILE), n_items), block(CH_TILE, all_single ? 1 : 8);
   if (is_bf16)
     causal_conv_act_kernel<bf16><<<grid, block, 0, stream>>>((const bf16*)x, ldx, taps, L, state, slot_stride, item_start,
