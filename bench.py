@@ -319,6 +319,55 @@ def run_prefill(engine, tokens, reps, rng):
     return ms
 
 
+def robazen_config(width, ff, layers, vocab):
+    """A Robazen model of real-looking layers at this width: gated-delta layers with heads of 128 (one key head for two
+    value heads), a parallel layer of attention (heads of 64, two per key head, chunks of 1,024 positions) beside time
+    mixing (heads of 64), a channel-wise delta layer; every layer with a feed-forward of `ff`; no loop."""
+    H = width // 128
+    delta = dict(conv=4, dim=128, heads=H, kv_heads=max(H // 2, 1), vdim=128)
+    par = dict(left=dict(dim=64, heads=width // 64, kv_heads=width // 128, mask=dict(size=1024), scale=0.125, softcap=30.0,
+                         vdim=64), right=dict(dim=64, heads=width // 64))
+    kinds = [("delta", delta), ("delta", delta), ("parallel", par), ("channel_delta", delta)]
+    return dict(architecture="Robazen", vocab=vocab, width=width, norm=dict(eps=1e-5),
+                layers=[dict(type=kinds[i % 4][0], mixer=kinds[i % 4][1], mlp=dict(ff=ff, kind="dense")) for i in range(layers)])
+
+
+def run_design(design, shapes, layers, batches, steps, warmup):
+    """Prefill and decode of the new design beside the LFM2 model of the same width, depth, feed-forward and
+    vocabulary (the closest model the engine has): random weights, the same measurements as the headline's."""
+    import numpy as np
+    import torch
+    from fellm_b200.config import EngineOptions
+    from fellm_b200.engine import Engine
+    out = {}
+    for shape in shapes:
+        lfm2, seed = shape_config(shape)
+        lfm2["num_hidden_layers"] = layers
+        lfm2["full_attn_idxs"] = [i for i in lfm2["full_attn_idxs"] if i < layers]
+        lfm2["block_auto_adjust_ff_dim"] = False
+        width, ff, vocab = lfm2["hidden_size"], lfm2["block_ff_dim"], lfm2["vocab_size"]
+        row = {}
+        for name, cfg in (("robazen", robazen_config(width, ff, layers, vocab)), ("lfm2", lfm2)):
+            ctx_end = PROMPT + warmup + steps + 80
+            opts = EngineOptions(dtype="bfloat16", n_ctx=ctx_end, ctx_past_model=True, n_batch=4096, n_ubatch=2048,
+                                 page_tokens=64, max_requests=max(batches), max_tokens=max(batches) * ctx_end, cuda_graphs=True)
+            engine = Engine.random(cfg, seed, opts)
+            rng = np.random.default_rng(seed)
+            r = {"weights_mb": model_bytes(engine) // 1000000}
+            ms = run_prefill(engine, PREFILL_TOKENS, 3, rng)
+            r["prefill"] = {"tokens": PREFILL_TOKENS, "ms": round(ms, 3), "tokens_per_s": round(PREFILL_TOKENS / ms * 1e3, 1)}
+            for b in batches:
+                v, ms, launches, _, c0, c1 = run_decode(engine, b, steps, warmup, rng, prompt=PROMPT,
+                                                        context_end=PROMPT + warmup + steps)
+                r[f"decode_b{b}"] = {"tokens_per_s": round(v, 1), "ms_per_step": round(ms, 4), "launches_per_step": launches // steps,
+                                     "contexts": [c0, c1]}
+            row[name] = r
+            del engine
+            torch.cuda.empty_cache()
+        out[f"width{width}_ff{ff}_layers{layers}"] = row
+    return out
+
+
 def run_mixed_workload(engine, rng, n_requests, max_new):
     """Prompts of 128..4,096 random ids through the scheduler (n_ubatch 512: prompt portions of up to
     512 tokens beside the decode tokens of the requests already generating), greedy, max_new tokens
@@ -468,6 +517,10 @@ def main():
                     help="with FELLM_B200_TRACE=1: write the kernel timeline of one decode step (--batch requests, or with --only prefill of one prefill step; "
                          "--context tokens each) to FILE and stop; not a bench value")
     ap.add_argument("--context", type=int, default=PROMPT)
+    ap.add_argument("--design", choices=["robazen"], default=None,
+                    help="prefill and decode throughput of this design at a few real-looking sizes beside the LFM2 model of "
+                         "equal width, depth and feed-forward (--layers layers, default 8; --steps decode steps, default 64); "
+                         "prints one line of its own and leaves the headline measurement alone")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -483,6 +536,15 @@ def main():
     from fellm_b200.engine import Engine
 
     hbm, tf_burst, tf_sus, src = peaks()
+    if args.design:
+        clocks = ClockSampler()
+        clocks.start()
+        steps = 64 if args.steps == 2048 else args.steps
+        sizes = run_design(args.design, ["350m", "1.2b"] if args.shape == "350m" else [args.shape], args.layers or 8,
+                           sorted({1, args.batch}), steps, max(args.warmup, 3))
+        print(json.dumps({"design": args.design, "dtype": "bf16", "data": "synthetic: random ids, random weights", "sizes": sizes,
+                          "clocks": clocks.stop()}))
+        return 0
     if args.workload:
         clocks = ClockSampler()
         clocks.start()

@@ -68,10 +68,12 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 // addresses of [keys][ROWB] tiles).  Thread (g = lane/4, c = lane%4) owns rows g and g+8; a key at
 // tile index i (absolute index key0 + i) counts for row r iff lo[r] <= key0 + i <= hi[r].
 // m, l: running maximum (log2 domain) and this thread's share of the running sum per row.
-template <int NKT, bool MASKED = true>
+// CAPPED: scores are soft-capped, cap * tanh(s * scale / cap), with cap_log2 = cap * log2(e).
+template <int NKT, bool MASKED = true, bool CAPPED = false>
 __device__ __forceinline__ void attend_tile(const unsigned (&qf)[KS][4], unsigned k_s, unsigned v_s, int key0,
                                             const int (&lo)[2], const int (&hi)[2], float scale_log2,
-                                            float (&o)[DN][4], float (&m)[2], float (&l)[2], int lane) {
+                                            float (&o)[DN][4], float (&m)[2], float (&l)[2], int lane,
+                                            float cap_log2 = 0.f) {
   const int c = lane & 3;
   float s[NKT][4];
 #pragma unroll
@@ -97,7 +99,9 @@ __device__ __forceinline__ void attend_tile(const unsigned (&qf)[KS][4], unsigne
     for (int e = 0; e < 4; ++e) {
       int key = key0 + n * 8 + 2 * c + (e & 1);
       int r = e >> 1;
-      float v = (!MASKED || (key >= lo[r] && key <= hi[r])) ? s[n][e] * scale_log2 : -INFINITY;
+      float sc = s[n][e] * scale_log2;
+      if (CAPPED) sc = cap_log2 * tanhf(sc / cap_log2);
+      float v = (!MASKED || (key >= lo[r] && key <= hi[r])) ? sc : -INFINITY;
       s[n][e] = v;
       mx[r] = fmaxf(mx[r], v);
     }
@@ -263,6 +267,12 @@ struct AttnArgs {
   bf16* out; float* scratch; int* counters;
   int max_pages, T, H, G, page_tokens, layer, layers_in_group, window, split_len, max_splits, n_items;
   float scale_log2;
+  // prefill only: queries read in place from rows of ldq elements, blocks of `chunk` positions a query does not look
+  // out of (0: none), a soft cap on the scores (cap * log2(e); 0: none), a gate per (row, head) whose sigmoid scales
+  // the head's output (null: none)
+  int ldq, chunk, ldg;
+  float cap_log2;
+  const float* gate;
 };
 
 __device__ __forceinline__ const bf16* key_row(const AttnArgs& a, const int* bt, int g, int key) {
@@ -315,12 +325,13 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(AttnAr
       int pos = pos0 + tok[r];
       hi[r] = valid[r] ? pos : -1;
       lo[r] = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+      if (a.chunk > 0) lo[r] = max(lo[r], (pos / a.chunk) * a.chunk);
       if (!valid[r]) lo[r] = 1 << 30;
     }
     unsigned qf[KS][4];
     load_q(qf, [&](int i) -> const bf16* {
       int rho = warp * 16 + i; int t = rho / R, h = rho - t * R;
-      return t < n_tok ? a.q + ((size_t)(row_begin + tok0 + t) * a.H + g * R + h) * HD : nullptr;
+      return t < n_tok ? a.q + (size_t)(row_begin + tok0 + t) * a.ldq + (size_t)(g * R + h) * HD : nullptr;
     }, lane);
 
     float o[DN][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
@@ -328,7 +339,8 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(AttnAr
     for (int d = 0; d < DN; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
 
     // keys of the whole block: from the first token's window start to the last token's position
-    const int k_first = (a.window > 0 && pos0 - a.window + 1 > 0) ? pos0 - a.window + 1 : 0;
+    int k_first = (a.window > 0 && pos0 - a.window + 1 > 0) ? pos0 - a.window + 1 : 0;
+    if (a.chunk > 0) k_first = max(k_first, (pos0 / a.chunk) * a.chunk);      // (the first token's block starts first)
     const int k_last = pos0 + n_tok - 1;
     const int n_tiles = (k_last - k_first) / PF_TK + 1;
     auto issue = [&](int j) {
@@ -360,8 +372,10 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(AttnAr
       int key0 = k_first + j * PF_TK;
       // a warp whose rows all end before this tile has nothing to add (warp-uniform test)
       int warp_hi = pos0 + min(n_tok - 1, (warp * 16 + 15) / R);
-      if (key0 <= warp_hi && warp * 16 < n_tok * R)
-        attend_tile<PF_TK / 8>(qf, ks, vs, key0, lo, hi, a.scale_log2, o, m, l, lane);
+      if (key0 <= warp_hi && warp * 16 < n_tok * R) {
+        if (a.cap_log2 > 0.f) attend_tile<PF_TK / 8, true, true>(qf, ks, vs, key0, lo, hi, a.scale_log2, o, m, l, lane, a.cap_log2);
+        else attend_tile<PF_TK / 8>(qf, ks, vs, key0, lo, hi, a.scale_log2, o, m, l, lane);
+      }
       __syncthreads();                                         // the stage is refilled by the next issue
     }
     cp_async_wait<0>();
@@ -371,6 +385,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(AttnAr
       l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
       if (!valid[r]) continue;
       float inv = 1.0f / l[r];
+      if (a.gate) inv *= 1.0f / (1.0f + expf(-a.gate[(size_t)(row_begin + tok0 + tok[r]) * a.ldg + g * R + hr[r]]));
       bf16* dst = a.out + ((size_t)(row_begin + tok0 + tok[r]) * a.H + g * R + hr[r]) * HD;
 #pragma unroll
       for (int d = 0; d < DN; ++d)
@@ -935,7 +950,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap pool_map, AttnA
     unsigned qf[KS][4];
     load_q(qf, [&](int i) -> const bf16* {
       int rho = warp * 16 + i; int t = rho / R, h = rho - t * R;
-      return t < n_tok ? a.q + ((size_t)(row_begin + tok0 + t) * a.H + g * R + h) * HD : nullptr;
+      return t < n_tok ? a.q + (size_t)(row_begin + tok0 + t) * a.ldq + (size_t)(g * R + h) * HD : nullptr;
     }, lane);
     float o[DN][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 #pragma unroll
@@ -992,6 +1007,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap pool_map, AttnA
       l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
       if (!valid[r]) continue;
       float inv = 1.0f / l[r];
+      if (a.gate) inv *= 1.0f / (1.0f + expf(-a.gate[(size_t)(row_begin + tok0 + tok[r]) * a.ldg + g * R + hr[r]]));
       bf16* dst = a.out + ((size_t)(row_begin + tok0 + tok[r]) * a.H + g * R + hr[r]) * HD;
 #pragma unroll
       for (int d = 0; d < DN; ++d)
@@ -1047,6 +1063,7 @@ static int fill_args(AttnArgs& a, const void* q, const void* pool, const int* bl
   a.page_tokens = page_tokens; a.layer = layer; a.layers_in_group = layers_in_group; a.window = window;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.item_start = nullptr; a.scratch = nullptr; a.counters = nullptr; a.split_len = 1; a.max_splits = 1; a.n_items = 0;
+  a.ldq = H * HD; a.chunk = 0; a.ldg = 0; a.cap_log2 = 0.f; a.gate = nullptr;
   return 0;
 }
 
@@ -1054,16 +1071,35 @@ FELLM_API int fellm_attn_head_dim() { return HD; }
 
 // q [T, H, hd], out [T, H*hd]; rows of item i are item_start[i]..item_start[i+1], its positions are
 // consecutive from positions[item_start[i]]; max_item_rows: the longest item of the step.
+// The general form: q rows ldq elements apart (heads at the row's start), a soft cap, chunks and a gate [T, ldg].
+FELLM_API int fellm_attn_prefill_mma_general(const void* q, int ldq, const void* pool, const int* block_table, int max_pages,
+                                             const int* positions, const int* row_slot, const int* item_start, int n_items,
+                                             int max_item_rows, void* out, int T, int H, int G, int hd, int page_tokens,
+                                             int layer, int layers_in_group, float scale, int window, int chunk,
+                                             float softcap, const float* gate, int ldg, cudaStream_t stream);
+
 FELLM_API int fellm_attn_prefill_mma(const void* q, const void* pool, const int* block_table, int max_pages,
                                      const int* positions, const int* row_slot, const int* item_start, int n_items,
                                      int max_item_rows, void* out, int T, int H, int G, int hd, int page_tokens,
                                      int layer, int layers_in_group, float scale, int window, cudaStream_t stream) {
+  return fellm_attn_prefill_mma_general(q, H * hd, pool, block_table, max_pages, positions, row_slot, item_start, n_items,
+                                        max_item_rows, out, T, H, G, hd, page_tokens, layer, layers_in_group, scale, window,
+                                        0, 0.f, nullptr, 0, stream);
+}
+
+FELLM_API int fellm_attn_prefill_mma_general(const void* q, int ldq, const void* pool, const int* block_table, int max_pages,
+                                             const int* positions, const int* row_slot, const int* item_start, int n_items,
+                                             int max_item_rows, void* out, int T, int H, int G, int hd, int page_tokens,
+                                             int layer, int layers_in_group, float scale, int window, int chunk,
+                                             float softcap, const float* gate, int ldg, cudaStream_t stream) {
   if (T <= 0 || n_items <= 0) return 0;
   AttnArgs a;
   int e = fill_args(a, q, pool, block_table, max_pages, positions, row_slot, out, T, H, G, hd, page_tokens, layer,
                     layers_in_group, scale, window);
   if (e) return e;
   if (!item_start) return FELLM_ERR_ARG;
+  if (ldq < H * hd || (ldq & 1) || chunk < 0 || softcap < 0.f) return FELLM_ERR_ARG;
+  a.ldq = ldq; a.chunk = chunk; a.cap_log2 = softcap * 1.4426950408889634f; a.gate = gate; a.ldg = ldg;
   int R = H / G;
   if (R > PF_WARPS * 16) return FELLM_ERR_SIZE;
   a.item_start = item_start; a.n_items = n_items;

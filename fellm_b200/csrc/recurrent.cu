@@ -25,8 +25,11 @@ __device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
 // ---------------------------------------------------------------- short causal convolution + activation
-// grid (channel tiles, items), block (CH_TILE, row lanes).  out[t, c] = act(sum_j taps[c, j] in[t - (L-1) + j, c]);
-// inputs before the portion come from the slot's history (the last L-1 inputs; zeros for a new request).
+// grid (channel tiles, items, row tiles), block (CH_TILE, row lanes).  out[t, c] = act(sum_j taps[c, j] in[t - (L-1) + j, c]);
+// inputs before the portion come from the slot's history (the last L-1 inputs; zeros for a new request).  The block of
+// row tile 0 is the only one that touches the slot: it reads the history before its rows and, behind a barrier, writes
+// the portion's last L-1 inputs there (no other block reads the slot, so no block can see the new history too early).
+#define ROW_TILE 64
 template <typename TA>
 __global__ void causal_conv_act_kernel(const TA* __restrict__ x, int ldx, const float* __restrict__ taps, int L,
                                        float* __restrict__ state, long long slot_stride,
@@ -36,28 +39,35 @@ __global__ void causal_conv_act_kernel(const TA* __restrict__ x, int ldx, const 
   const int item = blockIdx.y, tx = threadIdx.x;
   const int c = blockIdx.x * CH_TILE + tx;
   const int r0 = item_start[item], n = item_start[item + 1] - r0;
+  const int tile0 = blockIdx.z * ROW_TILE;
+  if (tile0 >= n && blockIdx.z > 0) return;
+  const bool first = blockIdx.z == 0;
   float* st = state + (size_t)item_slot[item] * slot_stride;
   const bool live = c < C;
-  if (threadIdx.y == 0 && live)
-    for (int j = 0; j < L - 1; ++j) hist[j][tx] = st[(size_t)j * C + c];
-  __syncthreads();
+  if (first) {
+    if (threadIdx.y == 0 && live)
+      for (int j = 0; j < L - 1; ++j) hist[j][tx] = st[(size_t)j * C + c];
+    __syncthreads();
+  }
   float w[MAX_TAPS];
 #pragma unroll
   for (int j = 0; j < MAX_TAPS; ++j) w[j] = (live && j < L) ? taps[(size_t)c * L + j] : 0.f;
   if (live) {
-    for (int r = threadIdx.y; r < n; r += blockDim.y) {
+    const int r_end = min(n, tile0 + ROW_TILE);
+    for (int r = tile0 + threadIdx.y; r < r_end; r += blockDim.y) {
       float acc = 0.f;
 #pragma unroll
       for (int j = 0; j < MAX_TAPS; ++j) {
         if (j < L) {
           int idx = r - (L - 1) + j;
-          float v = idx >= 0 ? to_f(x[(size_t)(r0 + idx) * ldx + c]) : hist[L - 1 + idx][tx];
+          float v = idx >= 0 ? to_f(x[(size_t)(r0 + idx) * ldx + c]) : hist[L - 1 + idx][tx];     // (idx < 0 only in row tile 0)
           acc = fmaf(w[j], v, acc);
         }
       }
       out[(size_t)(r0 + r) * ldo + c] = from_f<TA>(act == 1 ? silu_f(acc) : acc);
     }
   }
+  if (!first) return;
   __syncthreads();
   if (threadIdx.y == 0 && live) {
     float keep[MAX_TAPS - 1];
@@ -76,11 +86,12 @@ __global__ void causal_conv_act_kernel(const TA* __restrict__ x, int ldx, const 
 
 FELLM_API int fellm_causal_conv_act(const void* x, int is_bf16, int ldx, const float* taps, int L, float* state,
                                     long long slot_stride, const int* item_start, const int* item_slot, void* out,
-                                    int ldo, int n_items, int C, int act, int all_single, cudaStream_t stream) {
+                                    int ldo, int n_items, int C, int act, int max_item_rows, cudaStream_t stream) {
   if (n_items <= 0 || C <= 0) return 0;
   if (L < 1 || L > MAX_TAPS) return FELLM_ERR_SIZE;
   if (!x || !taps || (!state && L > 1) || !item_start || !item_slot || !out) return FELLM_ERR_ARG;
-  dim3 grid(ceil_div(C, CH_TILE), n_items), block(CH_TILE, all_single ? 1 : 8);
+  if (max_item_rows < 1) max_item_rows = 1;
+  dim3 grid(ceil_div(C, CH_TILE), n_items, ceil_div(max_item_rows, ROW_TILE)), block(CH_TILE, max_item_rows == 1 ? 1 : 8);
   if (is_bf16)
     causal_conv_act_kernel<bf16><<<grid, block, 0, stream>>>((const bf16*)x, ldx, taps, L, state, slot_stride, item_start,
                                                              item_slot, (bf16*)out, ldo, C, act);
@@ -92,7 +103,7 @@ FELLM_API int fellm_causal_conv_act(const void* x, int is_bf16, int ldx, const f
 
 // ---------------------------------------------------------------- token shift
 // out[s][t][c] = h[t][c] + (h[t-1][c] - h[t][c]) * mu[s][c]; the row before a portion is the slot's state, which
-// then takes the portion's last row.  Same grid as the convolution.
+// then takes the portion's last row.  Same grid as the convolution; row tile 0 reads the slot and then writes it.
 template <typename TA>
 __global__ void token_shift_mix_kernel(const TA* __restrict__ h, const float* __restrict__ mu, int n_mix,
                                        float* __restrict__ state, long long slot_stride,
@@ -102,24 +113,29 @@ __global__ void token_shift_mix_kernel(const TA* __restrict__ h, const float* __
   const int c = blockIdx.x * CH_TILE + threadIdx.x;
   if (c >= d) return;
   const int r0 = item_start[item], n = item_start[item + 1] - r0;
+  const int tile0 = blockIdx.z * ROW_TILE;
+  if (tile0 >= n) return;
   float* st = state + (size_t)item_slot[item] * slot_stride;
-  const float first_prev = threadIdx.y == 0 ? st[c] : 0.f;     // row 0 belongs to row lane 0, which is also the one writer below
-  for (int r = threadIdx.y; r < n; r += blockDim.y) {
+  const bool owner = blockIdx.z == 0 && threadIdx.y == 0;       // row 0 is this thread's, and so is the slot
+  const float first_prev = owner ? st[c] : 0.f;
+  const int r_end = min(n, tile0 + ROW_TILE);
+  for (int r = tile0 + threadIdx.y; r < r_end; r += blockDim.y) {
     float cur = to_f(h[(size_t)(r0 + r) * d + c]);
     float prev = r > 0 ? to_f(h[(size_t)(r0 + r - 1) * d + c]) : first_prev;
     float diff = prev - cur;
     for (int s = 0; s < n_mix; ++s)
       out[((size_t)s * T + r0 + r) * d + c] = from_f<TA>(fmaf(diff, mu[(size_t)s * d + c], cur));
   }
-  if (threadIdx.y == 0 && n > 0) st[c] = to_f(h[(size_t)(r0 + n - 1) * d + c]);
+  if (owner) st[c] = to_f(h[(size_t)(r0 + n - 1) * d + c]);
 }
 
 FELLM_API int fellm_token_shift_mix(const void* h, int is_bf16, const float* mu, int n_mix, float* state,
                                     long long slot_stride, const int* item_start, const int* item_slot, void* out,
-                                    int T, int n_items, int d, int all_single, cudaStream_t stream) {
+                                    int T, int n_items, int d, int max_item_rows, cudaStream_t stream) {
   if (n_items <= 0 || d <= 0) return 0;
   if (!h || !mu || !state || !item_start || !item_slot || !out || n_mix < 1) return FELLM_ERR_ARG;
-  dim3 grid(ceil_div(d, CH_TILE), n_items), block(CH_TILE, all_single ? 1 : 8);
+  if (max_item_rows < 1) max_item_rows = 1;
+  dim3 grid(ceil_div(d, CH_TILE), n_items, ceil_div(max_item_rows, ROW_TILE)), block(CH_TILE, max_item_rows == 1 ? 1 : 8);
   if (is_bf16)
     token_shift_mix_kernel<bf16><<<grid, block, 0, stream>>>((const bf16*)h, mu, n_mix, state, slot_stride, item_start,
                                                              item_slot, (bf16*)out, T, d);
@@ -185,202 +201,262 @@ FELLM_API int fellm_lowrank_expand(const float* z, int ldz, const void* W2, int 
 }
 
 // ---------------------------------------------------------------- the two scans
-// A warp owns CPW = 32 / KS columns of one head's matrix S [dk, dv]; a column's dk rows are spread over KS lanes
-// (row i = ks + KS * r, r < RMAX), so that a thread keeps at most RMAX values.  Columns are independent of one
-// another in both recurrences; sums over dk run over r in a thread, then over the KS lanes by a butterfly.
-#define RMAX 32
+// One kernel for both recurrences.  Per head the state is a matrix S [dk, dv]; its columns do not meet, so a
+// warp owns CPW = 32 / KS of them and spreads a column's dk rows over KS lanes, four rows at a time (row
+// 4 (ks + KS r4) + e belongs to lane ks: a float4 of the staged vectors per lane, consecutive lanes on consecutive
+// float4s).  Sums over dk run over (r4, e) in a thread, then over the KS lanes by a butterfly.
+//
+// Both recurrences have the form, per token and column j,
+//     d1 = sum_i S[i,j] A_i        d2 = sum_i S[i,j] B_i          (from the state BEFORE the token)
+//     u  = beta (v_j - d1)   (delta rule)       or   u = v_j      (decay and bonus)
+//     o_j = d2 + u c
+//     S[i,j] <- G_i S[i,j] + K_i u
+// with per-token vectors A, B, G, K [dk] and scalars beta, c that do not depend on S:
+//   delta rule (k^ = k / |k|, q^ = q / |q| / sqrt(dk), decay g per head or per channel):
+//       A = g k^,  B = g q^,  G = g,  K = k^,  c = k^ . q^      (S^T q after the write = g S^T q + u (k.q))
+//   decay and bonus:  B = r,  G = w,  K = k,  c = sum_i r_i u_i k_i,  A unused
+// so the chain from token to token is one reduction and one multiply-add per element.  Four producer warps stage
+// these vectors for the next SC_TOK tokens (loads, unit norms, decays, sigmoids) in shared memory while four
+// consumer warps run the chain over the tokens staged before: one block barrier per stage.
+#define SC_CONSUMERS 4
+#define SC_PRODUCERS 4
+#define SC_THREADS ((SC_CONSUMERS + SC_PRODUCERS) * 32)
+#define SC_MAX_TOK 16
 
-__device__ __forceinline__ float group_sum(float v, int ks_lanes) {
-  for (int o = 1; o < ks_lanes; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  return v;
+struct ScanArgs {
+  // delta rule: q at qkv, k at qkv + k_off, v at qkv + v_off of a row (ld elements); decay and bonus: r, k, v rows
+  const void* q; const void* k; const void* v; int ld, k_off, v_off;
+  const float* small; int lds, b_off, a_off;           // delta: beta's logit (and the per-head decay's)
+  const float* A_log; const float* dt_bias;            // delta, decay per head
+  const float* gch;                                    // delta per channel: g; decay and bonus: w   [T, H*dk]
+  const float* bonus;                                  // decay and bonus: u [H, dk]
+  float* state; long long slot_stride;
+  const int* item_start; const int* item_slot;
+  float* out;
+  int H, G, dk, dv, KS, tc;
+};
+
+__device__ __forceinline__ void producers_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(SC_PRODUCERS * 32) : "memory");
+}
+
+// The producers' share of a stage.  First the raw vectors of all its tokens, every thread with several loads in flight
+// (a token's vectors are short: taken token by token, each load's latency would stand alone); then, behind a barrier of
+// the producers, a warp per token turns them into A, B, G, K and the token's scalars.
+template <int MODE, typename TA>
+__device__ __forceinline__ void scan_stage(const ScanArgs& a, float* buf, int DKP, int COLS, int h, int col0, int row0,
+                                           int n_tok, int ptid) {
+  float* A = buf; float* B = A + a.tc * DKP; float* Gd = B + a.tc * DKP; float* KK = Gd + a.tc * DKP;
+  float* V = KK + a.tc * DKP; float* beta = V + a.tc * COLS; float* cc = beta + a.tc;
+  const int dk = a.dk;
+  constexpr int PT = SC_PRODUCERS * 32, U = 4;
+  const int total = n_tok * DKP;
+  const int g = MODE == 2 ? h : h / (a.H / a.G);
+  const TA* x0p = (const TA*)a.q + (size_t)g * dk;                                         // q, or r
+  const TA* x1p = MODE == 2 ? (const TA*)a.k + (size_t)h * dk : x0p + a.k_off;             // k
+  const float* x2p = MODE == 0 ? nullptr : a.gch + (size_t)h * dk;                          // the decay per channel
+  for (int base = ptid; base < total; base += PT * U) {
+    float x0[U], x1[U], x2[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int idx = base + u * PT;
+      x0[u] = x1[u] = x2[u] = 0.f;
+      if (idx < total) {
+        const int t = idx / DKP, i = idx - t * DKP;
+        if (i < dk) {
+          const size_t row = (size_t)(row0 + t);
+          x0[u] = to_f(x0p[row * a.ld + i]);
+          x1[u] = to_f(x1p[row * a.ld + i]);
+          if (MODE != 0) x2[u] = x2p[row * ((size_t)a.H * dk) + i];
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int idx = base + u * PT;
+      if (idx < total) { B[idx] = x0[u]; KK[idx] = x1[u]; Gd[idx] = x2[u]; }
+    }
+  }
+  const TA* vp = MODE == 2 ? (const TA*)a.v + (size_t)h * dk : (const TA*)a.q + a.v_off + (size_t)h * a.dv;
+  for (int idx = ptid; idx < n_tok * COLS; idx += PT) {
+    const int t = idx / COLS, x = idx - t * COLS;
+    V[idx] = col0 + x < a.dv ? to_f(vp[(size_t)(row0 + t) * a.ld + col0 + x]) : 0.f;
+  }
+  producers_sync();
+  const int pw = ptid >> 5, lane = ptid & 31;
+  for (int t = pw; t < n_tok; t += SC_PRODUCERS) {
+    const size_t row = (size_t)(row0 + t);
+    float* At = A + t * DKP; float* Bt = B + t * DKP; float* Gt = Gd + t * DKP; float* Kt = KK + t * DKP;
+    if (MODE == 2) {
+      const float* ur = a.bonus + (size_t)h * dk;
+      float c = 0.f;
+      for (int i = lane; i < dk; i += 32) c = fmaf(Bt[i] * ur[i], Kt[i], c);
+      c = warp_sum(c);
+      if (lane == 0) { cc[t] = c; beta[t] = 1.f; }
+    } else {
+      float sq = 0.f, sk = 0.f, kq = 0.f;
+      for (int i = lane; i < DKP; i += 32) {
+        const float q = Bt[i], k = Kt[i];
+        sq = fmaf(q, q, sq); sk = fmaf(k, k, sk); kq = fmaf(k, q, kq);
+      }
+      sq = warp_sum(sq); sk = warp_sum(sk); kq = warp_sum(kq);
+      const float kn = 1.0f / sqrtf(sk + 1e-6f);
+      const float qn = 1.0f / (sqrtf(sq + 1e-6f) * sqrtf((float)dk));
+      float gs = 0.f;
+      if (MODE == 0) gs = expf(-expf(a.A_log[h]) * softplus_f(a.small[row * a.lds + a.a_off + h] + a.dt_bias[h]));
+      for (int i = lane; i < DKP; i += 32) {
+        const float kk = Kt[i] * kn, qq = Bt[i] * qn;
+        const float gi = MODE == 1 ? Gt[i] : gs;
+        At[i] = gi * kk; Bt[i] = gi * qq; Gt[i] = gi; Kt[i] = kk;
+      }
+      if (lane == 0) { cc[t] = kq * kn * qn; beta[t] = sigmoid_f(a.small[row * a.lds + a.b_off + h]); }
+    }
+  }
+}
+
+template <int MODE, int R4, typename TA>
+__global__ void __launch_bounds__(SC_THREADS) scan_kernel(ScanArgs a) {
+  extern __shared__ __align__(16) float sc_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int KS = a.KS, CPW = 32 / KS, COLS = SC_CONSUMERS * CPW, DKP = 4 * KS * R4;
+  const int col_tiles = (a.dv + COLS - 1) / COLS;
+  const int h = blockIdx.x / col_tiles, col0 = (blockIdx.x - h * col_tiles) * COLS;
+  const int item = blockIdx.y;
+  const int row_begin = a.item_start[item], n = a.item_start[item + 1] - row_begin;
+  const int per_buf = a.tc * (4 * DKP + COLS + 4);          // (a multiple of four floats: the second buffer stays 16-byte aligned)
+  const bool consumer = warp < SC_CONSUMERS;
+  const int ks = lane % KS, cw = warp * CPW + lane / KS;          // (consumers) this thread's lane of rows and column
+  const int j = col0 + cw;
+  const bool live = consumer && j < a.dv;
+  float* Sg = a.state + (size_t)a.item_slot[item] * a.slot_stride + (size_t)h * a.dk * a.dv;
+  float S[4 * R4];
+  if (consumer) {
+#pragma unroll
+    for (int r4 = 0; r4 < R4; ++r4)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        int i = 4 * (ks + KS * r4) + e;
+        S[4 * r4 + e] = (live && i < a.dk) ? Sg[(size_t)i * a.dv + j] : 0.f;
+      }
+  }
+  const int n_stages = (n + a.tc - 1) / a.tc;
+  if (!consumer) scan_stage<MODE, TA>(a, sc_smem, DKP, COLS, h, col0, row_begin, min(a.tc, n), (int)threadIdx.x - SC_CONSUMERS * 32);
+  __syncthreads();
+  for (int s = 0; s < n_stages; ++s) {
+    float* buf = sc_smem + (s & 1) * per_buf;
+    const int t0 = s * a.tc, n_tok = min(a.tc, n - t0);
+    if (!consumer) {
+      if (s + 1 < n_stages)
+        scan_stage<MODE, TA>(a, sc_smem + ((s + 1) & 1) * per_buf, DKP, COLS, h, col0, row_begin + t0 + a.tc,
+                             min(a.tc, n - t0 - a.tc), (int)threadIdx.x - SC_CONSUMERS * 32);
+    } else {
+      const float4* A4 = (const float4*)buf;
+      const float4* B4 = (const float4*)(buf + a.tc * DKP);
+      const float4* G4 = (const float4*)(buf + 2 * a.tc * DKP);
+      const float4* K4 = (const float4*)(buf + 3 * a.tc * DKP);
+      const float* V = buf + 4 * a.tc * DKP;
+      const float* beta = V + a.tc * COLS;
+      const float* cc = beta + a.tc;
+      const int dq = DKP / 4;
+      for (int t = 0; t < n_tok; ++t) {
+        float p1[4] = {0.f, 0.f, 0.f, 0.f}, p2[4] = {0.f, 0.f, 0.f, 0.f};      // four short chains a dot, added in a fixed order
+#pragma unroll
+        for (int r4 = 0; r4 < R4; ++r4) {
+          const float4 b = B4[t * dq + ks + KS * r4];
+          p2[0] = fmaf(S[4 * r4], b.x, p2[0]); p2[1] = fmaf(S[4 * r4 + 1], b.y, p2[1]);
+          p2[2] = fmaf(S[4 * r4 + 2], b.z, p2[2]); p2[3] = fmaf(S[4 * r4 + 3], b.w, p2[3]);
+          if (MODE != 2) {
+            const float4 av = A4[t * dq + ks + KS * r4];
+            p1[0] = fmaf(S[4 * r4], av.x, p1[0]); p1[1] = fmaf(S[4 * r4 + 1], av.y, p1[1]);
+            p1[2] = fmaf(S[4 * r4 + 2], av.z, p1[2]); p1[3] = fmaf(S[4 * r4 + 3], av.w, p1[3]);
+          }
+        }
+        float d1 = (p1[0] + p1[1]) + (p1[2] + p1[3]), d2 = (p2[0] + p2[1]) + (p2[2] + p2[3]);
+        for (int o = 1; o < KS; o <<= 1) {
+          d2 += __shfl_xor_sync(0xffffffffu, d2, o);
+          if (MODE != 2) d1 += __shfl_xor_sync(0xffffffffu, d1, o);
+        }
+        const float v = V[t * COLS + cw];
+        const float u = MODE == 2 ? v : beta[t] * (v - d1);
+        const float o = fmaf(u, cc[t], d2);
+#pragma unroll
+        for (int r4 = 0; r4 < R4; ++r4) {
+          const float4 gv = G4[t * dq + ks + KS * r4];
+          const float4 kv = K4[t * dq + ks + KS * r4];
+          S[4 * r4] = fmaf(kv.x, u, gv.x * S[4 * r4]);
+          S[4 * r4 + 1] = fmaf(kv.y, u, gv.y * S[4 * r4 + 1]);
+          S[4 * r4 + 2] = fmaf(kv.z, u, gv.z * S[4 * r4 + 2]);
+          S[4 * r4 + 3] = fmaf(kv.w, u, gv.w * S[4 * r4 + 3]);
+        }
+        if (ks == 0 && live) a.out[(size_t)(row_begin + t0 + t) * ((size_t)a.H * a.dv) + (size_t)h * a.dv + j] = o;
+      }
+    }
+    __syncthreads();
+  }
+  if (live) {
+#pragma unroll
+    for (int r4 = 0; r4 < R4; ++r4)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        int i = 4 * (ks + KS * r4) + e;
+        if (i < a.dk) Sg[(size_t)i * a.dv + j] = S[4 * r4 + e];
+      }
+  }
+}
+
+template <int MODE, typename TA>
+static int scan_launch(ScanArgs& a, int n_items, cudaStream_t stream) {
+  int KS = 1;
+  while (KS < 32 && a.dk > 16 * KS) KS <<= 1;                // up to 16 rows a thread while dk <= 512
+  int r4 = (a.dk + 4 * KS - 1) / (4 * KS), R4 = 1;
+  while (R4 < r4) R4 <<= 1;
+  if (R4 > 8) return FELLM_ERR_SIZE;
+  a.KS = KS;
+  const int CPW = 32 / KS, COLS = SC_CONSUMERS * CPW, DKP = 4 * KS * R4;
+  const int per_tok = (4 * DKP + COLS + 4) * (int)sizeof(float);
+  int tc = 40960 / per_tok;
+  a.tc = tc < 1 ? 1 : (tc > SC_MAX_TOK ? SC_MAX_TOK : tc);
+  const size_t smem = (size_t)2 * a.tc * per_tok;
+  dim3 grid(a.H * ((a.dv + COLS - 1) / COLS), n_items);
+  void (*kern)(ScanArgs) = R4 == 1 ? scan_kernel<MODE, 1, TA> : R4 == 2 ? scan_kernel<MODE, 2, TA>
+                         : R4 == 4 ? scan_kernel<MODE, 4, TA> : scan_kernel<MODE, 8, TA>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  kern<<<grid, SC_THREADS, smem, stream>>>(a);
+  return launch_status();
 }
 
 // Gated delta rule.  qkv [T, ldq]: q heads at column 0 (G x dk), k at k_off, v at v_off (H x dv), after their
 // convolutions and SiLU.  small [T, lds]: beta's logit at column b_off + h; per-head decay: logit at a_off + h,
 // g = exp(-exp(A_log[h]) softplus(logit + dt_bias[h])); per-channel decay: gch [T, H*dk] holds g itself.
-template <typename TA>
-__global__ void __launch_bounds__(128)
-delta_scan_kernel(const TA* __restrict__ qkv, int ldq, int k_off, int v_off, const float* __restrict__ small, int lds,
-                  int b_off, int a_off, const float* __restrict__ A_log, const float* __restrict__ dt_bias,
-                  const float* __restrict__ gch, float* __restrict__ state, long long slot_stride,
-                  const int* __restrict__ item_start, const int* __restrict__ item_slot, float* __restrict__ out,
-                  int H, int G, int dk, int dv, int KS, int col_groups) {
-  const int warp = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  const int item = blockIdx.y;
-  if (warp >= H * col_groups) return;
-  const int h = warp / col_groups, cg = warp - h * col_groups;
-  const int CPW = 32 / KS, ks = lane % KS;
-  const int j = cg * CPW + lane / KS;
-  const bool col_live = j < dv;
-  const int jc = col_live ? j : dv - 1;
-  const int g = h / (H / G);
-  const int r0 = item_start[item], n = item_start[item + 1] - r0;
-  float* Sg = state + (size_t)item_slot[item] * slot_stride + (size_t)h * dk * dv;
-  float S[RMAX];
-#pragma unroll
-  for (int r = 0; r < RMAX; ++r) {
-    int i = ks + KS * r;
-    S[r] = i < dk ? Sg[(size_t)i * dv + jc] : 0.f;
-  }
-  const float rate = gch ? 0.f : expf(A_log[h]);
-  const float bias_a = gch ? 0.f : dt_bias[h];
-  const float q_scale = 1.0f / sqrtf((float)dk);
-  for (int t = 0; t < n; ++t) {
-    const size_t row = (size_t)(r0 + t);
-    const TA* qr = qkv + row * ldq + (size_t)g * dk;
-    const TA* kr = qr + k_off;
-    float q[RMAX], k[RMAX];
-    float sq = 0.f, sk = 0.f;
-#pragma unroll
-    for (int r = 0; r < RMAX; ++r) {
-      int i = ks + KS * r;
-      q[r] = i < dk ? to_f(qr[i]) : 0.f;
-      k[r] = i < dk ? to_f(kr[i]) : 0.f;
-      sq = fmaf(q[r], q[r], sq);
-      sk = fmaf(k[r], k[r], sk);
-    }
-    sq = group_sum(sq, KS);
-    sk = group_sum(sk, KS);
-    const float qn = q_scale / sqrtf(sq + 1e-6f), kn = 1.0f / sqrtf(sk + 1e-6f);
-    const float v = to_f(qkv[row * ldq + v_off + (size_t)h * dv + jc]);
-    const float beta = sigmoid_f(small[row * lds + b_off + h]);
-    float dot = 0.f;
-    if (gch) {
-      const float* gr = gch + row * ((size_t)H * dk) + (size_t)h * dk;
-#pragma unroll
-      for (int r = 0; r < RMAX; ++r) {
-        int i = ks + KS * r;
-        k[r] *= kn;
-        S[r] *= i < dk ? gr[i] : 0.f;
-        dot = fmaf(S[r], k[r], dot);
-      }
-    } else {
-      const float gt = expf(-rate * softplus_f(small[row * lds + a_off + h] + bias_a));
-#pragma unroll
-      for (int r = 0; r < RMAX; ++r) {
-        k[r] *= kn;
-        S[r] *= gt;
-        dot = fmaf(S[r], k[r], dot);
-      }
-    }
-    dot = group_sum(dot, KS);
-    const float u = beta * (v - dot);
-    float o = 0.f;
-#pragma unroll
-    for (int r = 0; r < RMAX; ++r) {
-      S[r] = fmaf(k[r], u, S[r]);
-      o = fmaf(S[r], q[r], o);
-    }
-    o = group_sum(o, KS) * qn;
-    if (ks == 0 && col_live) out[row * ((size_t)H * dv) + (size_t)h * dv + j] = o;
-  }
-  if (col_live) {
-#pragma unroll
-    for (int r = 0; r < RMAX; ++r) {
-      int i = ks + KS * r;
-      if (i < dk) Sg[(size_t)i * dv + j] = S[r];
-    }
-  }
-}
-
-static int scan_lanes(int dk) {
-  int ks = 1;
-  while (ks * RMAX < dk) ks <<= 1;
-  return ks;
-}
-
 FELLM_API int fellm_delta_scan(const void* qkv, int is_bf16, int ldq, int k_off, int v_off, const float* small, int lds,
                                int b_off, int a_off, const float* A_log, const float* dt_bias, const float* gch,
                                float* state, long long slot_stride, const int* item_start, const int* item_slot,
                                float* out, int n_items, int H, int G, int dk, int dv, cudaStream_t stream) {
   if (n_items <= 0) return 0;
-  if (dk < 1 || dk > 32 * RMAX || dv < 1 || G < 1 || H % G) return FELLM_ERR_SIZE;
+  if (dk < 1 || dk > 1024 || dv < 1 || G < 1 || H % G) return FELLM_ERR_SIZE;
   if (!qkv || !small || !state || !item_start || !item_slot || !out || (!gch && (!A_log || !dt_bias))) return FELLM_ERR_ARG;
-  const int KS = scan_lanes(dk), CPW = 32 / KS;
-  const int col_groups = ceil_div(dv, CPW);
-  const int warps = H * col_groups;
-  dim3 grid(ceil_div(warps, 4), n_items);
-  if (is_bf16)
-    delta_scan_kernel<bf16><<<grid, 128, 0, stream>>>((const bf16*)qkv, ldq, k_off, v_off, small, lds, b_off, a_off, A_log,
-                                                      dt_bias, gch, state, slot_stride, item_start, item_slot, out, H, G, dk,
-                                                      dv, KS, col_groups);
-  else
-    delta_scan_kernel<float><<<grid, 128, 0, stream>>>((const float*)qkv, ldq, k_off, v_off, small, lds, b_off, a_off, A_log,
-                                                       dt_bias, gch, state, slot_stride, item_start, item_slot, out, H, G, dk,
-                                                       dv, KS, col_groups);
-  return launch_status();
+  ScanArgs a = {};
+  a.q = qkv; a.ld = ldq; a.k_off = k_off; a.v_off = v_off; a.small = small; a.lds = lds; a.b_off = b_off; a.a_off = a_off;
+  a.A_log = A_log; a.dt_bias = dt_bias; a.gch = gch; a.state = state; a.slot_stride = slot_stride;
+  a.item_start = item_start; a.item_slot = item_slot; a.out = out; a.H = H; a.G = G; a.dk = dk; a.dv = dv;
+  if (gch) return is_bf16 ? scan_launch<1, bf16>(a, n_items, stream) : scan_launch<1, float>(a, n_items, stream);
+  return is_bf16 ? scan_launch<0, bf16>(a, n_items, stream) : scan_launch<0, float>(a, n_items, stream);
 }
 
 // Decay-and-bonus recurrence.  r, k, v [T, ld] (H x dk each), w float32 [T, H*dk] (the decay itself), u [H, dk].
-template <typename TA>
-__global__ void __launch_bounds__(128)
-decay_bonus_scan_kernel(const TA* __restrict__ rr, const TA* __restrict__ kk, const TA* __restrict__ vv, int ld,
-                        const float* __restrict__ w, const float* __restrict__ u, float* __restrict__ state,
-                        long long slot_stride, const int* __restrict__ item_start, const int* __restrict__ item_slot,
-                        float* __restrict__ out, int H, int dk, int KS, int col_groups) {
-  const int warp = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  const int item = blockIdx.y;
-  if (warp >= H * col_groups) return;
-  const int h = warp / col_groups, cg = warp - h * col_groups;
-  const int CPW = 32 / KS, ks = lane % KS;
-  const int j = cg * CPW + lane / KS;
-  const bool col_live = j < dk;
-  const int jc = col_live ? j : dk - 1;
-  const int r0 = item_start[item], n = item_start[item + 1] - r0;
-  float* Sg = state + (size_t)item_slot[item] * slot_stride + (size_t)h * dk * dk;
-  float S[RMAX], bonus[RMAX];
-#pragma unroll
-  for (int r = 0; r < RMAX; ++r) {
-    int i = ks + KS * r;
-    S[r] = i < dk ? Sg[(size_t)i * dk + jc] : 0.f;
-    bonus[r] = i < dk ? u[(size_t)h * dk + i] : 0.f;
-  }
-  for (int t = 0; t < n; ++t) {
-    const size_t row = (size_t)(r0 + t);
-    const size_t base = row * ld + (size_t)h * dk;
-    const float* wr = w + row * ((size_t)H * dk) + (size_t)h * dk;
-    const float vj = to_f(vv[base + jc]);
-    float o = 0.f;
-#pragma unroll
-    for (int r = 0; r < RMAX; ++r) {
-      int i = ks + KS * r;
-      if (i < dk) {
-        float kv = to_f(kk[base + i]) * vj;
-        o = fmaf(to_f(rr[base + i]), fmaf(bonus[r], kv, S[r]), o);
-        S[r] = fmaf(wr[i], S[r], kv);
-      }
-    }
-    o = group_sum(o, KS);
-    if (ks == 0 && col_live) out[row * ((size_t)H * dk) + (size_t)h * dk + j] = o;
-  }
-  if (col_live) {
-#pragma unroll
-    for (int r = 0; r < RMAX; ++r) {
-      int i = ks + KS * r;
-      if (i < dk) Sg[(size_t)i * dk + j] = S[r];
-    }
-  }
-}
-
 FELLM_API int fellm_decay_bonus_scan(const void* r, const void* k, const void* v, int is_bf16, int ld, const float* w,
                                      const float* u, float* state, long long slot_stride, const int* item_start,
                                      const int* item_slot, float* out, int n_items, int H, int dk, cudaStream_t stream) {
   if (n_items <= 0) return 0;
-  if (dk < 1 || dk > 32 * RMAX || H < 1) return FELLM_ERR_SIZE;
+  if (dk < 1 || dk > 1024 || H < 1) return FELLM_ERR_SIZE;
   if (!r || !k || !v || !w || !u || !state || !item_start || !item_slot || !out) return FELLM_ERR_ARG;
-  const int KS = scan_lanes(dk), CPW = 32 / KS;
-  const int col_groups = ceil_div(dk, CPW);
-  dim3 grid(ceil_div(H * col_groups, 4), n_items);
-  if (is_bf16)
-    decay_bonus_scan_kernel<bf16><<<grid, 128, 0, stream>>>((const bf16*)r, (const bf16*)k, (const bf16*)v, ld, w, u, state,
-                                                            slot_stride, item_start, item_slot, out, H, dk, KS, col_groups);
-  else
-    decay_bonus_scan_kernel<float><<<grid, 128, 0, stream>>>((const float*)r, (const float*)k, (const float*)v, ld, w, u,
-                                                             state, slot_stride, item_start, item_slot, out, H, dk, KS,
-                                                             col_groups);
-  return launch_status();
+  ScanArgs a = {};
+  a.q = r; a.k = k; a.v = v; a.ld = ld; a.gch = w; a.bonus = u; a.state = state; a.slot_stride = slot_stride;
+  a.item_start = item_start; a.item_slot = item_slot; a.out = out; a.H = H; a.G = H; a.dk = dk; a.dv = dk;
+  return is_bf16 ? scan_launch<2, bf16>(a, n_items, stream) : scan_launch<2, float>(a, n_items, stream);
 }
 
 // ---------------------------------------------------------------- per-head norm and gate

@@ -308,7 +308,7 @@ def gemm_bf16_conv(x, w_blocked, bias, conv_w, conv_bias, state, row_slot, *, no
 
 # ------------------------------------------------------------------------------ recurrent mixers
 
-MAX_SCAN_KEY_DIM = 1024
+MAX_SCAN_KEY_DIM = 1024          # 32 lanes x 32 rows of a column
 
 
 def _state_args(state):
@@ -316,9 +316,10 @@ def _state_args(state):
     return _p(state), state.stride(0)
 
 
-def causal_conv_act(x, taps, state, item_start, item_slot, n_items, all_single, act="silu", out=None):
+def causal_conv_act(x, taps, state, item_start, item_slot, n_items, max_item_rows, act="silu", out=None):
     """x [T, C] (row stride free) -> act(causal conv over time per channel), taps float32 [C, L] (last column: the
-    current token); state float32 [slots, L-1, C]: the inputs before each portion, moved on by the call."""
+    current token); state float32 [slots, L-1, C]: the inputs before each portion, moved on by the call.
+    max_item_rows: the longest portion of the step (the grid covers that many rows of every item)."""
     _dev(x, taps, state, item_start, item_slot)
     T, C = x.shape
     L = taps.shape[1]
@@ -333,11 +334,11 @@ def causal_conv_act(x, taps, state, item_start, item_slot, n_items, all_single, 
     f = _fn("recurrent", "fellm_causal_conv_act",
             [_c_p, _c_int, _c_int, _c_p, _c_int, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p])
     _check(f(_p(x), _is_bf16(x), x.stride(0), _p(taps), L, sp, ss, _p(item_start), _p(item_slot), _p(out), out.stride(0),
-             n_items, C, {"none": 0, "silu": 1}[act], int(all_single), _stream()), "causal_conv_act")
+             n_items, C, {"none": 0, "silu": 1}[act], int(max_item_rows), _stream()), "causal_conv_act")
     return out
 
 
-def token_shift_mix(h, mu, state, item_start, item_slot, n_items, all_single, out=None):
+def token_shift_mix(h, mu, state, item_start, item_slot, n_items, max_item_rows, out=None):
     """h [T, d], mu float32 [S, d] -> [S, T, d]: h + (h_prev - h) * mu_s, h_prev the row before (the slot's state
     float32 [slots, d] before a portion's first row; the state then takes the portion's last row)."""
     _dev(h, mu, state, item_start, item_slot)
@@ -352,7 +353,7 @@ def token_shift_mix(h, mu, state, item_start, item_slot, n_items, all_single, ou
     f = _fn("recurrent", "fellm_token_shift_mix",
             [_c_p, _c_int, _c_p, _c_int, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_p])
     _check(f(_p(h), _is_bf16(h), _p(mu), S, sp, ss, _p(item_start), _p(item_slot), _p(out), T, n_items, d,
-             int(all_single), _stream()), "token_shift_mix")
+             int(max_item_rows), _stream()), "token_shift_mix")
     return out
 
 
@@ -1052,6 +1053,7 @@ USE_TMA_DECODE = os.environ.get("FELLM_B200_TMA_DECODE", "1") != "0"
 FUSE_DECODE_ROPE = os.environ.get("FELLM_B200_FUSE_ROPE", "1") != "0"
 USE_TMA_PREFILL = os.environ.get("FELLM_B200_TMA_PREFILL", "1") != "0"
 USE_UMMA_PREFILL = os.environ.get("FELLM_B200_UMMA_ATTN", "1") != "0"
+GENERAL_ATTENTION_MMA = os.environ.get("FELLM_B200_GENERAL_ATTN_MMA", "1") != "0"     # capped / chunked / gated prefill on tensor cores
 UMMA_PREFILL_MIN_ROWS = int(os.environ.get("FELLM_B200_UMMA_ATTN_MIN_ROWS", 1))    # (token, head) rows of the longest item
 
 
@@ -1187,6 +1189,32 @@ def attention_prefill(q, pool, block_table, positions, row_slot, item_start, n_i
     _check(f(_p(q), _p(pool), _p(block_table), block_table.shape[1], _p(positions), _p(row_slot), _p(item_start),
              n_items, max_item_rows, _p(out), T, H, G, hd, page_tokens, layer, pool.shape[1], float(scale),
              int(window or 0), _stream()), "attention_prefill")
+    return out
+
+
+def attention_prefill_general(qkv, H, pool, block_table, positions, row_slot, item_start, n_items, max_item_rows, layer,
+                              scale, *, window=None, chunk=None, softcap=None, gate=None, out=None):
+    """Portions of prompts on tensor cores (bfloat16; keys and values of one size, the one the library is compiled
+    for) with the part's soft cap, chunks and gate: q is read in place from rows [T, >= H*hd] (heads at column 0),
+    gate float32 [T, >= H].  pool [pages, layers, 2, G, page_tokens, hd]."""
+    _dev(qkv, pool, block_table, positions, row_slot, item_start, gate)
+    T = qkv.shape[0]
+    G, page_tokens, hd = pool.shape[3], pool.shape[4], pool.shape[5]
+    if qkv.dtype != torch.bfloat16 or pool.dtype != torch.bfloat16 or hd % 16 or not 16 <= hd <= 256 or H % G or H // G > 64:
+        raise KernelError("attention_prefill_general takes bfloat16, head sizes of a multiple of 16 in 16..256, up to 64 heads a kv head")
+    assert qkv.stride(1) == 1 and qkv.stride(0) % 2 == 0 and pool.is_contiguous()
+    _i32(block_table, "block_table"), _i32(positions, "positions"), _i32(row_slot, "row_slot"), _i32(item_start, "item_start")
+    if gate is not None:
+        assert gate.dtype == torch.float32 and gate.stride(1) == 1
+    if out is None:
+        out = torch.empty((T, H * hd), dtype=torch.bfloat16, device=qkv.device)
+    f = _fn("attention_mma", "fellm_attn_prefill_mma_general",
+            [_c_p, _c_int, _c_p, _c_p, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+             _c_int, _c_int, _c_f, _c_int, _c_int, _c_f, _c_p, _c_int, _c_p], defines={"HD": hd})
+    _check(f(_p(qkv), qkv.stride(0), _p(pool), _p(block_table), block_table.shape[1], _p(positions), _p(row_slot),
+             _p(item_start), n_items, max_item_rows, _p(out), T, H, G, hd, page_tokens, layer, pool.shape[1], float(scale),
+             int(window or 0), int(chunk or 0), float(softcap or 0.0), _p(gate), gate.stride(0) if gate is not None else 0,
+             _stream()), "attention_prefill_general")
     return out
 
 

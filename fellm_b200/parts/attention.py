@@ -128,16 +128,27 @@ class Attention(Mixer):
         qkv = linear(xn, self.w["qkv.weight"])
         ops.kv_write(qkv, H * hd, (H + G) * hd, cache.pool, cache.block_table, ctx.positions, ctx.row_slot, cache.layer,
                      cache.page_tokens, G, hd, vd, status=ctx.status)
-        a = ops.paged_attention_general(qkv, H, hd, vd, cache.pool, cache.block_table, ctx.positions, ctx.row_slot,
-                                        cache.layer, cache.page_tokens, G, self.scale, window=self.window,
-                                        chunk=self.chunk, softcap=self.softcap, gate=gate)
+        if self._on_tensor_cores(qkv) and not ctx.all_single:
+            # portions of prompts: the tensor-core kernel (keys and values of one size)
+            a = ops.attention_prefill_general(qkv, H, cache.pool, cache.block_table, ctx.positions, ctx.row_slot,
+                                              ctx.item_start, ctx.n_items, ctx.max_item_rows, cache.layer, self.scale,
+                                              window=self.window, chunk=self.chunk, softcap=self.softcap, gate=gate)
+        else:
+            a = ops.paged_attention_general(qkv, H, hd, vd, cache.pool, cache.block_table, ctx.positions, ctx.row_slot,
+                                            cache.layer, cache.page_tokens, G, self.scale, window=self.window,
+                                            chunk=self.chunk, softcap=self.softcap, gate=gate)
         linear(a, self.w["out_proj.weight"], out=out, accumulate=True)
         return out
+
+    def _on_tensor_cores(self, qkv) -> bool:
+        return (qkv.dtype == torch.bfloat16 and self.vd == self.hd and self.hd % 16 == 0 and self.H // self.G <= 64
+                and ops.GENERAL_ATTENTION_MMA)
 
     def weight_order(self):
         return [self.w["qkv.weight"], self.w["out_proj.weight"]]
 
     def kernel_modules(self, dtype):
         if self.general:
-            return linear_modules(dtype) + [("attention_simt", None)]
+            mma = dtype == "bfloat16" and self.vd == self.hd and self.hd % 16 == 0 and self.H // self.G <= 64
+            return linear_modules(dtype) + [("attention_simt", None)] + ([("attention_mma", {"HD": self.hd})] if mma else [])
         return linear_modules(dtype) + [("qk_rope_write", None)] + ops.attention_modules(dtype, self.hd)

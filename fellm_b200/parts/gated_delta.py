@@ -126,7 +126,7 @@ class GatedDelta(Mixer):
         big = linear(xn, w["big.weight"])                                   # [T, q | k | v (| g)]
         small = linear(xn, w["small.weight"], out_dtype=torch.float32)      # [T, b | a or a1 (| g1)] float32
         qkv = ops.causal_conv_act(big[:, :self.n_conv], w["taps"], conv_state.states, ctx.item_start,
-                                  conv_state.item_slot, ctx.n_items, ctx.all_single, act="silu")
+                                  conv_state.item_slot, ctx.n_items, ctx.max_item_rows, act="silu")
         a_off = self.small_offs[1]
         gch = None
         if self.decay == "channel":

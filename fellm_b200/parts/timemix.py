@@ -60,7 +60,7 @@ class TimeMix(Mixer):
         shift_state, mat_state = cache
         w = self.w
         mixes = ops.token_shift_mix(xn, w["mu"], shift_state.states, ctx.item_start, shift_state.item_slot,
-                                    ctx.n_items, ctx.all_single)
+                                    ctx.n_items, ctx.max_item_rows)
         r = linear(mixes[0], w["r.weight"])
         k = linear(mixes[1], w["k.weight"])
         v = linear(mixes[2], w["v.weight"])

@@ -54,13 +54,13 @@ def test_short_convolution_in_portions_equals_one_pass(taps):
     portion is shorter than the history; two requests side by side in slots of their own."""
     from fellm_b200 import ops
     g = torch.Generator().manual_seed(taps)
-    C, T = 70, 41
+    C, T = 70, 241                                  # the last portion is longer than a block's tile of rows
     x = [torch.randn(T, C, generator=g) for _ in range(2)]
     w = torch.randn(C, taps, generator=g)
     want = [F.silu(P.causal_short_conv(xi.double(), w.double())) for xi in x]
     state = torch.zeros(5, max(taps - 1, 0), C, device=DEV)
     state[:] = 7.0                                  # other slots' contents must not matter
-    cuts = [1, 2, 1, 5, 2, 9, 1, 20]
+    cuts = [1, 2, 1, 5, 2, 9, 1, 20, 200]
     at = 0
     for n in cuts:
         starts, slots_t, slots = _items([n, n])
@@ -68,7 +68,7 @@ def test_short_convolution_in_portions_equals_one_pass(taps):
             for s in slots:
                 state[s].zero_()
         rows = torch.cat([x[0][at:at + n], x[1][at:at + n]]).to(DEV)
-        got = ops.causal_conv_act(rows, w.to(DEV), state, starts, slots_t, 2, n == 1)
+        got = ops.causal_conv_act(rows, w.to(DEV), state, starts, slots_t, 2, n)
         for i in range(2):
             d = (got[i * n:(i + 1) * n].double().cpu() - want[i][at:at + n]).abs().max()
             assert d < 1e-5, (taps, at, n, i, float(d))
@@ -79,15 +79,15 @@ def test_short_convolution_in_portions_equals_one_pass(taps):
 def test_token_shift_in_portions():
     from fellm_b200 import ops
     g = torch.Generator().manual_seed(3)
-    d, T = 50, 23
+    d, T = 50, 223
     h = torch.randn(T, d, generator=g)
     mu = torch.rand(5, d, generator=g)
     prev = torch.cat([torch.zeros(1, d), h[:-1]])
     want = torch.stack([h + (prev - h) * mu[s] for s in range(5)])
     state = torch.zeros(4, d, device=DEV)
     at = 0
-    for n in [1, 2, 7, 1, 12]:
-        got = ops.token_shift_mix(h[at:at + n].to(DEV).contiguous(), mu.to(DEV), state, _i32([0, n]), _i32([1]), 1, n == 1)
+    for n in [1, 2, 7, 1, 12, 200]:
+        got = ops.token_shift_mix(h[at:at + n].to(DEV).contiguous(), mu.to(DEV), state, _i32([0, n]), _i32([1]), 1, n)
         assert (got.cpu() - want[:, at:at + n]).abs().max() < 1e-6
         at += n
 
@@ -283,6 +283,55 @@ def test_attention_at_the_edges_of_chunks_and_pages(dtype, chunk, page):
         assert (got - want).abs().max() < tol * max(1.0, float(want.abs().max())), (r, float((got - want).abs().max()))
 
 
+@pytest.mark.parametrize("hd,chunk,page,softcap", [(16, 24, 16, 9.0), (64, 100, 64, None), (48, 7, 16, 30.0), (32, 64, 32, 2.0)])
+def test_tensor_core_attention_of_portions_with_cap_chunk_and_gate(hd, chunk, page, softcap):
+    """The tensor-core kernel for portions (keys and values of one size) against the plain attention: three items of
+    unequal length in one launch, each continuing a request at a position inside a chunk and inside a page."""
+    from fellm_b200 import ops
+    H, G = 6, 2
+    g = torch.Generator().manual_seed(hd + chunk)
+    cfg = dict(heads=H, kv_heads=G, dim=hd, vdim=hd, scale=0.4, mask=dict(size=chunk))
+    if softcap:
+        cfg["softcap"] = softcap
+    lens, done = [70, 1, 33], [chunk + 3, 2 * page - 1, 0]                 # tokens of this step, tokens already in the cache
+    n_pages = [-(-(a + b) // page) for a, b in zip(lens, done)]
+    pool = torch.zeros(sum(n_pages) + 1, 2, 2, G, page, hd, dtype=torch.bfloat16, device=DEV)
+    table = torch.full((3, max(n_pages)), -1, dtype=torch.int32, device=DEV)
+    perm = torch.randperm(sum(n_pages), generator=g).to(torch.int32)
+    at = 0
+    for r in range(3):
+        table[r, :n_pages[r]] = perm[at:at + n_pages[r]]
+        at += n_pages[r]
+    rows, gates, wants, pos, slot, starts = [], [], [], [], [], [0]
+    layer = 1
+    for r in range(3):
+        T = lens[r] + done[r]
+        qkv = (torch.randn(T, (H + 2 * G) * hd + 8, generator=g) * 1.5).bfloat16()
+        gate = torch.randn(T, H + 3, generator=g)
+        q, k, v = qkv[:, :(H + 2 * G) * hd].float().split([H * hd, G * hd, G * hd], 1)
+        wants.append(_attention_from_qkv(q, k, v, gate[:, :H], cfg)[done[r]:])
+        dev = qkv.to(DEV)
+        if done[r]:                     # what earlier steps left in the cache
+            ops.kv_write(dev[:done[r]], H * hd, (H + G) * hd, pool, table, _i32(list(range(done[r]))), _i32([r] * done[r]),
+                         layer, page, G, hd, hd)
+        rows.append(dev[done[r]:])
+        gates.append(gate[done[r]:])
+        pos += list(range(done[r], T))
+        slot += [r] * lens[r]
+        starts.append(starts[-1] + lens[r])
+    qkv_d, gate_d = torch.cat(rows).contiguous(), torch.cat(gates).to(DEV).contiguous()
+    pos_d, slot_d = _i32(pos), _i32(slot)
+    ops.kv_write(qkv_d, H * hd, (H + G) * hd, pool, table, pos_d, slot_d, layer, page, G, hd, hd)
+    got = ops.attention_prefill_general(qkv_d, H, pool, table, pos_d, slot_d, _i32(starts), 3, max(lens), layer, 0.4,
+                                        chunk=chunk, softcap=softcap, gate=gate_d).double().cpu()
+    want = torch.cat(wants)
+    assert (got - want).abs().max() < 2e-2 * max(1.0, float(want.abs().max())), float((got - want).abs().max())
+    # and the kernel on CUDA cores gives the same on the same cache
+    simt = ops.paged_attention_general(qkv_d, H, hd, hd, pool, table, pos_d, slot_d, layer, page, G, 0.4, chunk=chunk,
+                                       softcap=softcap, gate=gate_d).double().cpu()
+    assert (simt - want).abs().max() < 2e-2 * max(1.0, float(want.abs().max()))
+
+
 def _attention_from_qkv(q, k, v, gate, cfg):
     H, G, hd, vd = cfg["heads"], cfg["kv_heads"], cfg["dim"], cfg["vdim"]
     T = q.shape[0]
@@ -463,6 +512,25 @@ def test_greedy_generation_through_the_scheduler(name):
                 break
             seq.append(got[k])
     assert all(s is not None for s in stats)
+
+
+def test_command_line_runs_the_design(capsys):
+    from fellm_b200 import cli
+    folder = U.model_folder("P")
+    assert cli.main(["inspect", "--model", folder]) == 0
+    out = capsys.readouterr().out
+    assert "architecture: Robazen" in out and "l0.mix.left.q" in out
+    assert cli.main(["run", folder, "--prompt", "5 17 3 9 100", "--max-tokens", "6", "--temperature", "0", "--dtype", "float32",
+                     "--page-tokens", "16", "-c", "256", "--kv-device-budget", "4194304"]) == 0
+    toks = [int(t) for t in capsys.readouterr().out.split()]
+    cfg, w = U.plain_model("P")
+    seq = [5, 17, 3, 9, 100]
+    for t in toks:
+        lg = P.forward(cfg, w, seq)[-1]
+        top = torch.topk(lg, 2).values
+        assert int(lg.argmax()) == t or float(top[0] - top[1]) < 1e-4 * float(lg.abs().max())
+        seq.append(t)
+    assert len(toks) == 6
 
 
 def test_bfloat16_generation_runs_through_the_entry_point():
