@@ -216,8 +216,10 @@ FELLM_API int fellm_lowrank_expand(const float* z, int ldz, const void* W2, int 
 //       A = g k^,  B = g q^,  G = g,  K = k^,  c = k^ . q^      (S^T q after the write = g S^T q + u (k.q))
 //   decay and bonus:  B = r,  G = w,  K = k,  c = sum_i r_i u_i k_i,  A unused
 // so the chain from token to token is one reduction and one multiply-add per element.  Four producer warps stage
-// these vectors for the next SC_TOK tokens (loads, unit norms, decays, sigmoids) in shared memory while four
-// consumer warps run the chain over the tokens staged before: one block barrier per stage.
+// these vectors for the next tokens (loads, unit norms, decays, sigmoids) in shared memory while four consumer
+// warps run the chain over the tokens staged before: one block barrier per stage.  KS is chosen from the model's
+// sizes alone (enough lanes a column that one prompt's columns fill the SMs), never from the batch: the order of
+// every sum is the same in every step.
 #define SC_CONSUMERS 4
 #define SC_PRODUCERS 4
 #define SC_THREADS ((SC_CONSUMERS + SC_PRODUCERS) * 32)
@@ -234,7 +236,18 @@ struct ScanArgs {
   const int* item_start; const int* item_slot;
   float* out;
   int H, G, dk, dv, KS, tc;
+  int vec;                                             // q, k (and the decay) can be read 16 bytes at a time
 };
+
+template <int VE> __device__ __forceinline__ void load_vec(const float* p, float* out) {
+  *(float4*)out = *(const float4*)p;
+}
+template <int VE> __device__ __forceinline__ void load_vec(const bf16* p, float* out) {
+  const uint4 raw = *(const uint4*)p;
+  const __nv_bfloat162* h = (const __nv_bfloat162*)&raw;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { float2 f = __bfloat1622float2(h[e]); out[2 * e] = f.x; out[2 * e + 1] = f.y; }
+}
 
 __device__ __forceinline__ void producers_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(SC_PRODUCERS * 32) : "memory");
@@ -255,6 +268,33 @@ __device__ __forceinline__ void scan_stage(const ScanArgs& a, float* buf, int DK
   const TA* x0p = (const TA*)a.q + (size_t)g * dk;                                         // q, or r
   const TA* x1p = MODE == 2 ? (const TA*)a.k + (size_t)h * dk : x0p + a.k_off;             // k
   const float* x2p = MODE == 0 ? nullptr : a.gch + (size_t)h * dk;                          // the decay per channel
+  if (a.vec) {
+    // eight (bfloat16) or four (float32) elements a load: 16 bytes of q, of k and, where there is one, of the decay
+    constexpr int VE = sizeof(TA) == 2 ? 8 : 4;
+    const int per_tok = DKP / VE, nvec = n_tok * per_tok;
+    for (int idx = ptid; idx < nvec; idx += PT) {
+      const int t = idx / per_tok, i = (idx - t * per_tok) * VE;
+      float x0[VE], x1[VE], x2[VE];
+#pragma unroll
+      for (int e = 0; e < VE; ++e) x0[e] = x1[e] = x2[e] = 0.f;
+      if (i < dk) {
+        const size_t row = (size_t)(row0 + t);
+        load_vec<VE>(x0p + row * a.ld + i, x0);
+        load_vec<VE>(x1p + row * a.ld + i, x1);
+        if (MODE != 0) {
+#pragma unroll
+          for (int e = 0; e < VE; e += 4) *(float4*)(x2 + e) = *(const float4*)(x2p + row * ((size_t)a.H * dk) + i + e);
+        }
+      }
+      const int o = t * DKP + i;
+#pragma unroll
+      for (int e = 0; e < VE; e += 4) {
+        *(float4*)(B + o + e) = *(float4*)(x0 + e);
+        *(float4*)(KK + o + e) = *(float4*)(x1 + e);
+        *(float4*)(Gd + o + e) = *(float4*)(x2 + e);
+      }
+    }
+  } else
   for (int base = ptid; base < total; base += PT * U) {
     float x0[U], x1[U], x2[U];
 #pragma unroll
@@ -282,10 +322,15 @@ __device__ __forceinline__ void scan_stage(const ScanArgs& a, float* buf, int DK
     const int t = idx / COLS, x = idx - t * COLS;
     V[idx] = col0 + x < a.dv ? to_f(vp[(size_t)(row0 + t) * a.ld + col0 + x]) : 0.f;
   }
+  if (MODE != 2 && ptid < n_tok) {              // the tokens' logits: beta's, and the decay's where it is one per head
+    const size_t row = (size_t)(row0 + ptid);
+    beta[ptid] = a.small[row * a.lds + a.b_off + h];
+    if (MODE == 0) cc[ptid] = a.small[row * a.lds + a.a_off + h];
+  }
   producers_sync();
   const int pw = ptid >> 5, lane = ptid & 31;
+  const float rate = MODE == 0 ? expf(a.A_log[h]) : 0.f, bias_a = MODE == 0 ? a.dt_bias[h] : 0.f;
   for (int t = pw; t < n_tok; t += SC_PRODUCERS) {
-    const size_t row = (size_t)(row0 + t);
     float* At = A + t * DKP; float* Bt = B + t * DKP; float* Gt = Gd + t * DKP; float* Kt = KK + t * DKP;
     if (MODE == 2) {
       const float* ur = a.bonus + (size_t)h * dk;
@@ -303,13 +348,14 @@ __device__ __forceinline__ void scan_stage(const ScanArgs& a, float* buf, int DK
       const float kn = 1.0f / sqrtf(sk + 1e-6f);
       const float qn = 1.0f / (sqrtf(sq + 1e-6f) * sqrtf((float)dk));
       float gs = 0.f;
-      if (MODE == 0) gs = expf(-expf(a.A_log[h]) * softplus_f(a.small[row * a.lds + a.a_off + h] + a.dt_bias[h]));
+      if (MODE == 0) gs = expf(-rate * softplus_f(cc[t] + bias_a));
       for (int i = lane; i < DKP; i += 32) {
         const float kk = Kt[i] * kn, qq = Bt[i] * qn;
         const float gi = MODE == 1 ? Gt[i] : gs;
         At[i] = gi * kk; Bt[i] = gi * qq; Gt[i] = gi; Kt[i] = kk;
       }
-      if (lane == 0) { cc[t] = kq * kn * qn; beta[t] = sigmoid_f(a.small[row * a.lds + a.b_off + h]); }
+      __syncwarp();
+      if (lane == 0) { cc[t] = kq * kn * qn; beta[t] = sigmoid_f(beta[t]); }
     }
   }
 }
@@ -358,17 +404,36 @@ __global__ void __launch_bounds__(SC_THREADS) scan_kernel(ScanArgs a) {
       const float* beta = V + a.tc * COLS;
       const float* cc = beta + a.tc;
       const int dq = DKP / 4;
+      // the vectors of token t + 1 are asked for before token t's chain starts: nothing of them depends on S
+      float4 nA[R4], nB[R4], nG[R4], nK[R4];
+      float nv, nbeta, ncc;
+      constexpr bool AHEAD = R4 <= 4;              // (with 32 rows a thread the second set of vectors would spill)
+      auto fetch = [&](int t) {
+#pragma unroll
+        for (int r4 = 0; r4 < R4; ++r4) {
+          const int at = t * dq + ks + KS * r4;
+          if (MODE != 2) nA[r4] = A4[at];
+          nB[r4] = B4[at]; nG[r4] = G4[at]; nK[r4] = K4[at];
+        }
+        nv = V[t * COLS + cw]; nbeta = beta[t]; ncc = cc[t];
+      };
+      if (AHEAD) fetch(0);
+#pragma unroll 2
       for (int t = 0; t < n_tok; ++t) {
+        if (!AHEAD) fetch(t);
+        float4 cA[R4], cB[R4], cG[R4], cK[R4];
+#pragma unroll
+        for (int r4 = 0; r4 < R4; ++r4) { if (MODE != 2) cA[r4] = nA[r4]; cB[r4] = nB[r4]; cG[r4] = nG[r4]; cK[r4] = nK[r4]; }
+        const float v = nv, bt = nbeta, ct = ncc;
+        if (AHEAD && t + 1 < n_tok) fetch(t + 1);
         float p1[4] = {0.f, 0.f, 0.f, 0.f}, p2[4] = {0.f, 0.f, 0.f, 0.f};      // four short chains a dot, added in a fixed order
 #pragma unroll
         for (int r4 = 0; r4 < R4; ++r4) {
-          const float4 b = B4[t * dq + ks + KS * r4];
-          p2[0] = fmaf(S[4 * r4], b.x, p2[0]); p2[1] = fmaf(S[4 * r4 + 1], b.y, p2[1]);
-          p2[2] = fmaf(S[4 * r4 + 2], b.z, p2[2]); p2[3] = fmaf(S[4 * r4 + 3], b.w, p2[3]);
+          p2[0] = fmaf(S[4 * r4], cB[r4].x, p2[0]); p2[1] = fmaf(S[4 * r4 + 1], cB[r4].y, p2[1]);
+          p2[2] = fmaf(S[4 * r4 + 2], cB[r4].z, p2[2]); p2[3] = fmaf(S[4 * r4 + 3], cB[r4].w, p2[3]);
           if (MODE != 2) {
-            const float4 av = A4[t * dq + ks + KS * r4];
-            p1[0] = fmaf(S[4 * r4], av.x, p1[0]); p1[1] = fmaf(S[4 * r4 + 1], av.y, p1[1]);
-            p1[2] = fmaf(S[4 * r4 + 2], av.z, p1[2]); p1[3] = fmaf(S[4 * r4 + 3], av.w, p1[3]);
+            p1[0] = fmaf(S[4 * r4], cA[r4].x, p1[0]); p1[1] = fmaf(S[4 * r4 + 1], cA[r4].y, p1[1]);
+            p1[2] = fmaf(S[4 * r4 + 2], cA[r4].z, p1[2]); p1[3] = fmaf(S[4 * r4 + 3], cA[r4].w, p1[3]);
           }
         }
         float d1 = (p1[0] + p1[1]) + (p1[2] + p1[3]), d2 = (p2[0] + p2[1]) + (p2[2] + p2[3]);
@@ -376,17 +441,14 @@ __global__ void __launch_bounds__(SC_THREADS) scan_kernel(ScanArgs a) {
           d2 += __shfl_xor_sync(0xffffffffu, d2, o);
           if (MODE != 2) d1 += __shfl_xor_sync(0xffffffffu, d1, o);
         }
-        const float v = V[t * COLS + cw];
-        const float u = MODE == 2 ? v : beta[t] * (v - d1);
-        const float o = fmaf(u, cc[t], d2);
+        const float u = MODE == 2 ? v : bt * (v - d1);
+        const float o = fmaf(u, ct, d2);
 #pragma unroll
         for (int r4 = 0; r4 < R4; ++r4) {
-          const float4 gv = G4[t * dq + ks + KS * r4];
-          const float4 kv = K4[t * dq + ks + KS * r4];
-          S[4 * r4] = fmaf(kv.x, u, gv.x * S[4 * r4]);
-          S[4 * r4 + 1] = fmaf(kv.y, u, gv.y * S[4 * r4 + 1]);
-          S[4 * r4 + 2] = fmaf(kv.z, u, gv.z * S[4 * r4 + 2]);
-          S[4 * r4 + 3] = fmaf(kv.w, u, gv.w * S[4 * r4 + 3]);
+          S[4 * r4] = fmaf(cK[r4].x, u, cG[r4].x * S[4 * r4]);
+          S[4 * r4 + 1] = fmaf(cK[r4].y, u, cG[r4].y * S[4 * r4 + 1]);
+          S[4 * r4 + 2] = fmaf(cK[r4].z, u, cG[r4].z * S[4 * r4 + 2]);
+          S[4 * r4 + 3] = fmaf(cK[r4].w, u, cG[r4].w * S[4 * r4 + 3]);
         }
         if (ks == 0 && live) a.out[(size_t)(row_begin + t0 + t) * ((size_t)a.H * a.dv) + (size_t)h * a.dv + j] = o;
       }
@@ -408,10 +470,22 @@ template <int MODE, typename TA>
 static int scan_launch(ScanArgs& a, int n_items, cudaStream_t stream) {
   int KS = 1;
   while (KS < 32 && a.dk > 16 * KS) KS <<= 1;                // up to 16 rows a thread while dk <= 512
+  // more lanes a column while one item's blocks do not fill the device and a lane keeps four rows or more
+  while (KS < 32 && 8 * KS <= a.dk && a.H * ((a.dv * KS + 32 * SC_CONSUMERS - 1) / (32 * SC_CONSUMERS)) < 120) KS <<= 1;
   int r4 = (a.dk + 4 * KS - 1) / (4 * KS), R4 = 1;
   while (R4 < r4) R4 <<= 1;
   if (R4 > 8) return FELLM_ERR_SIZE;
   a.KS = KS;
+  {
+    const int ve = sizeof(TA) == 2 ? 8 : 4;
+    const size_t esz = sizeof(TA);
+    bool ok = a.dk % ve == 0 && a.ld % ve == 0 && (4 * KS * R4) % ve == 0 && ((uintptr_t)a.q % 16) == 0;
+    if (MODE == 2) ok = ok && ((uintptr_t)a.k % 16) == 0;
+    else ok = ok && a.k_off % ve == 0;
+    if (MODE != 0) ok = ok && ((uintptr_t)a.gch % 16) == 0;
+    (void)esz;
+    a.vec = ok ? 1 : 0;
+  }
   const int CPW = 32 / KS, COLS = SC_CONSUMERS * CPW, DKP = 4 * KS * R4;
   const int per_tok = (4 * DKP + COLS + 4) * (int)sizeof(float);
   int tc = 40960 / per_tok;
