@@ -32,7 +32,7 @@ RUN_DEFAULTS = dict(  # fellm.toml [run]
 
 
 def _parser():
-    ap = argparse.ArgumentParser(prog="fellm", description="fellm_b200: LFM2 inference on one B200")
+    ap = argparse.ArgumentParser(prog="fellm", description="fellm_b200: inference on one B200 (LFM2, Robazen)")
     ap.add_argument("--config", help="TOML file with a [run] table (FeLLM's fellm.toml layout)")
     ap.add_argument("--log", default=None, choices=sorted(LOG_LEVELS), help="log level of the fellm_b200 logger (stderr)")
     sub = ap.add_subparsers(dest="cmd", required=True)

@@ -33,7 +33,10 @@ class Attention(Mixer):
         self.size, self.H, self.G, self.hd = int(size), int(heads), int(kv_heads), int(head_dim)
         if self.H % self.G:
             raise ConfigError(f"attention: {self.H} heads are not a multiple of {self.G} kv heads")
-        if self.hd % 16 or not 16 <= self.hd <= 256:
+        general = bool(softcap or chunk or head_gate or (v_dim is not None and int(v_dim) != self.hd))
+        if general and not 1 <= self.hd <= 256:
+            raise ConfigError(f"attention: head_dim {self.hd} must be in 1..256")
+        if not general and (self.hd % 16 or not 16 <= self.hd <= 256):       # the tensor-core kernels' sizes
             raise ConfigError(f"attention: head_dim {self.hd} must be a multiple of 16 in 16..256")
         self.qk_norm, self.eps = bool(qk_norm), float(norm_eps)
         self.window = None if window is None else int(window)

@@ -49,7 +49,8 @@ class TimeMix(Mixer):
         self.rank = w["w1.weight"].shape[0]
         if w["w2.weight"].shape[1] != self.rank:
             raise WeightError(f"time_mix: the decay's factors have ranks {self.rank} and {w['w2.weight'].shape[1]}")
-        w["w1.weight"] = _pad_rows(w["w1.weight"])
+        for name in ("r.weight", "k.weight", "v.weight", "g.weight", "w1.weight"):
+            w[name] = _pad_rows(w[name])        # whole groups of output columns for the products' vector stores
 
     def cache_need(self):
         return [FixedState((self.size,)), FixedState((self.H, self.dk, self.dk))]
@@ -61,10 +62,11 @@ class TimeMix(Mixer):
         w = self.w
         mixes = ops.token_shift_mix(xn, w["mu"], shift_state.states, ctx.item_start, shift_state.item_slot,
                                     ctx.n_items, ctx.max_item_rows)
-        r = linear(mixes[0], w["r.weight"])
-        k = linear(mixes[1], w["k.weight"])
-        v = linear(mixes[2], w["v.weight"])
-        g = linear(mixes[3], w["g.weight"])
+        n = self.H * self.dk
+        r = linear(mixes[0], w["r.weight"])[:, :n]
+        k = linear(mixes[1], w["k.weight"])[:, :n]
+        v = linear(mixes[2], w["v.weight"])[:, :n]
+        g = linear(mixes[3], w["g.weight"])[:, :n]
         z = linear(mixes[4], w["w1.weight"], out_dtype=torch.float32)
         decay = ops.lowrank_expand(z[:, :self.rank], w["w2.weight"], w["w0"], f_in="tanh", f_out="exp_neg_exp")
         o = ops.decay_bonus_scan(r, k, v, decay, w["u"], mat_state.states, ctx.item_start, mat_state.item_slot,

@@ -53,7 +53,15 @@ CFG_R = dict(architecture="Robazen", vocab=128, width=64, norm=dict(eps=1e-5), l
     layer("parallel", parallel(2, 1, 64, 96, 32, 0.15, 40.0, 2, 32), ff=96),
 ], loop=dict(start=0, stop=2, times=2))
 
-CONFIGS = {"P": (CFG_P, 11), "Q": (CFG_Q, 12), "R": (CFG_R, 13)}
+# S: sizes that are multiples of nothing: key sizes 5 and 20, value sizes 7 and 12, three heads, 15 time-mix channels,
+# a vocabulary of 101, one convolution tap, a loop of one pass over the last layer
+CFG_S = dict(architecture="Robazen", vocab=101, width=72, norm=dict(eps=1e-5), layers=[
+    layer("delta", delta(3, 3, 5, 7, 1), ff=40),
+    layer("parallel", parallel(3, 1, 20, 12, 9, 0.22, 15.0, 3, 5), ff=None),
+    layer("channel_delta", delta(6, 2, 10, 3, 5), ff=24),
+], loop=dict(start=2, stop=3, times=1))
+
+CONFIGS = {"P": (CFG_P, 11), "Q": (CFG_Q, 12), "R": (CFG_R, 13), "S": (CFG_S, 14)}
 _tmp = tempfile.TemporaryDirectory(prefix="fellm_b200_robazen_")
 
 

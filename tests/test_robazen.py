@@ -121,7 +121,7 @@ def test_plain_mechanisms():
     assert torch.allclose(a[4], 0.5 * h[3:5].mean(0)) and torch.allclose(a[3], 0.5 * h[3]) and torch.allclose(a[2], 0.5 * h[:3].mean(0))
 
 
-@pytest.mark.parametrize("name", ["P", "Q", "R"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "S"])
 def test_written_folder_is_read_back_and_runs_in_the_plain_implementation(name):
     cfg, w = U.plain_model(name)
     assert cfg == U.CONFIGS[name][0]

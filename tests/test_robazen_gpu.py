@@ -362,7 +362,7 @@ def engines(request):
     made.clear()
 
 
-@pytest.mark.parametrize("name", ["P", "Q", "R"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "S"])
 def test_whole_prompt(engines, name):
     T = 150
     eng = engines(name)
@@ -410,7 +410,7 @@ def test_prompt_against_token_by_token(engines, name):
 
 
 @pytest.mark.parametrize("name,cuts", [("P", [2, 2, 3, 17, 2, 24, 1, 1, 23, 2, 48]), ("Q", [7, 2, 71, 2, 9, 80, 3]),
-                                       ("R", [31, 2, 1, 32, 33, 2])])
+                                       ("R", [31, 2, 1, 32, 33, 2]), ("S", [8, 2, 9, 1, 10, 65])])
 def test_portions_of_many_sizes(engines, name, cuts):
     T = 170
     eng = engines(name)
