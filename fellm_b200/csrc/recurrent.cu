@@ -215,13 +215,13 @@ FELLM_API int fellm_lowrank_expand(const float* z, int ldz, const void* W2, int 
 //   delta rule (k^ = k / |k|, q^ = q / |q| / sqrt(dk), decay g per head or per channel):
 //       A = g k^,  B = g q^,  G = g,  K = k^,  c = k^ . q^      (S^T q after the write = g S^T q + u (k.q))
 //   decay and bonus:  B = r,  G = w,  K = k,  c = sum_i r_i u_i k_i,  A unused
-// so the chain from token to token is one reduction and one multiply-add per element.  Four producer warps stage
+// so the chain from token to token is one reduction and one multiply-add per element.  Eight producer warps stage
 // these vectors for the next tokens (loads, unit norms, decays, sigmoids) in shared memory while four consumer
 // warps run the chain over the tokens staged before: one block barrier per stage.  KS is chosen from the model's
 // sizes alone (enough lanes a column that one prompt's columns fill the SMs), never from the batch: the order of
 // every sum is the same in every step.
 #define SC_CONSUMERS 4
-#define SC_PRODUCERS 4
+#define SC_PRODUCERS 8
 #define SC_THREADS ((SC_CONSUMERS + SC_PRODUCERS) * 32)
 #define SC_MAX_TOK 16
 
@@ -268,6 +268,26 @@ __device__ __forceinline__ void scan_stage(const ScanArgs& a, float* buf, int DK
   const TA* x0p = (const TA*)a.q + (size_t)g * dk;                                         // q, or r
   const TA* x1p = MODE == 2 ? (const TA*)a.k + (size_t)h * dk : x0p + a.k_off;             // k
   const float* x2p = MODE == 0 ? nullptr : a.gch + (size_t)h * dk;                          // the decay per channel
+  // The values of this block's columns and the tokens' logits are asked for first and stored last: their latency
+  // runs under the vectors' loads.
+  constexpr int VMAX = (SC_MAX_TOK * 32 * SC_CONSUMERS + PT - 1) / PT;
+  const TA* vp = MODE == 2 ? (const TA*)a.v + (size_t)h * dk : (const TA*)a.q + a.v_off + (size_t)h * a.dv;
+  float vreg[VMAX];
+#pragma unroll
+  for (int u = 0; u < VMAX; ++u) {
+    const int idx = ptid + u * PT;
+    vreg[u] = 0.f;
+    if (idx < n_tok * COLS) {
+      const int t = idx / COLS, x = idx - t * COLS;
+      if (col0 + x < a.dv) vreg[u] = to_f(vp[(size_t)(row0 + t) * a.ld + col0 + x]);
+    }
+  }
+  float logit_b = 0.f, logit_a = 0.f;
+  if (MODE != 2 && ptid < n_tok) {
+    const size_t row = (size_t)(row0 + ptid);
+    logit_b = a.small[row * a.lds + a.b_off + h];
+    if (MODE == 0) logit_a = a.small[row * a.lds + a.a_off + h];
+  }
   if (a.vec) {
     // eight (bfloat16) or four (float32) elements a load: 16 bytes of q, of k and, where there is one, of the decay
     constexpr int VE = sizeof(TA) == 2 ? 8 : 4;
@@ -294,59 +314,84 @@ __device__ __forceinline__ void scan_stage(const ScanArgs& a, float* buf, int DK
         *(float4*)(Gd + o + e) = *(float4*)(x2 + e);
       }
     }
-  } else
-  for (int base = ptid; base < total; base += PT * U) {
-    float x0[U], x1[U], x2[U];
+  } else {
+    for (int base = ptid; base < total; base += PT * U) {
+      float x0[U], x1[U], x2[U];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int idx = base + u * PT;
-      x0[u] = x1[u] = x2[u] = 0.f;
-      if (idx < total) {
-        const int t = idx / DKP, i = idx - t * DKP;
-        if (i < dk) {
-          const size_t row = (size_t)(row0 + t);
-          x0[u] = to_f(x0p[row * a.ld + i]);
-          x1[u] = to_f(x1p[row * a.ld + i]);
-          if (MODE != 0) x2[u] = x2p[row * ((size_t)a.H * dk) + i];
+      for (int u = 0; u < U; ++u) {
+        const int idx = base + u * PT;
+        x0[u] = x1[u] = x2[u] = 0.f;
+        if (idx < total) {
+          const int t = idx / DKP, i = idx - t * DKP;
+          if (i < dk) {
+            const size_t row = (size_t)(row0 + t);
+            x0[u] = to_f(x0p[row * a.ld + i]);
+            x1[u] = to_f(x1p[row * a.ld + i]);
+            if (MODE != 0) x2[u] = x2p[row * ((size_t)a.H * dk) + i];
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int idx = base + u * PT;
+        if (idx < total) { B[idx] = x0[u]; KK[idx] = x1[u]; Gd[idx] = x2[u]; }
+      }
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < VMAX; ++u) {
+    const int idx = ptid + u * PT;
+    if (idx < n_tok * COLS) V[idx] = vreg[u];
+  }
+  if (MODE != 2 && ptid < n_tok) { beta[ptid] = logit_b; cc[ptid] = logit_a; }
+  producers_sync();
+  // a warp takes TPW tokens at once: their sums and butterflies are independent chains
+  constexpr int TPW = SC_MAX_TOK / SC_PRODUCERS;
+  const int pw = ptid >> 5, lane = ptid & 31;
+  const float rate = MODE == 0 ? expf(a.A_log[h]) : 0.f, bias_a = MODE == 0 ? a.dt_bias[h] : 0.f;
+  if (MODE == 2) {
+    const float* ur = a.bonus + (size_t)h * dk;
+    float c[TPW];
+#pragma unroll
+    for (int u = 0; u < TPW; ++u) c[u] = 0.f;
+    for (int i = lane; i < dk; i += 32) {
+      const float b = ur[i];
+#pragma unroll
+      for (int u = 0; u < TPW; ++u) {
+        const int t = pw + u * SC_PRODUCERS;
+        if (t < n_tok) c[u] = fmaf(B[t * DKP + i] * b, KK[t * DKP + i], c[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < TPW; ++u) c[u] = warp_sum(c[u]);
+#pragma unroll
+    for (int u = 0; u < TPW; ++u) {
+      const int t = pw + u * SC_PRODUCERS;
+      if (t < n_tok && lane == 0) { cc[t] = c[u]; beta[t] = 1.f; }
+    }
+  } else {
+    float sq[TPW], sk[TPW], kq[TPW];
+#pragma unroll
+    for (int u = 0; u < TPW; ++u) sq[u] = sk[u] = kq[u] = 0.f;
+    for (int i = lane; i < DKP; i += 32) {
+#pragma unroll
+      for (int u = 0; u < TPW; ++u) {
+        const int t = pw + u * SC_PRODUCERS;
+        if (t < n_tok) {
+          const float q = B[t * DKP + i], k = KK[t * DKP + i];
+          sq[u] = fmaf(q, q, sq[u]); sk[u] = fmaf(k, k, sk[u]); kq[u] = fmaf(k, q, kq[u]);
         }
       }
     }
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int idx = base + u * PT;
-      if (idx < total) { B[idx] = x0[u]; KK[idx] = x1[u]; Gd[idx] = x2[u]; }
-    }
-  }
-  const TA* vp = MODE == 2 ? (const TA*)a.v + (size_t)h * dk : (const TA*)a.q + a.v_off + (size_t)h * a.dv;
-  for (int idx = ptid; idx < n_tok * COLS; idx += PT) {
-    const int t = idx / COLS, x = idx - t * COLS;
-    V[idx] = col0 + x < a.dv ? to_f(vp[(size_t)(row0 + t) * a.ld + col0 + x]) : 0.f;
-  }
-  if (MODE != 2 && ptid < n_tok) {              // the tokens' logits: beta's, and the decay's where it is one per head
-    const size_t row = (size_t)(row0 + ptid);
-    beta[ptid] = a.small[row * a.lds + a.b_off + h];
-    if (MODE == 0) cc[ptid] = a.small[row * a.lds + a.a_off + h];
-  }
-  producers_sync();
-  const int pw = ptid >> 5, lane = ptid & 31;
-  const float rate = MODE == 0 ? expf(a.A_log[h]) : 0.f, bias_a = MODE == 0 ? a.dt_bias[h] : 0.f;
-  for (int t = pw; t < n_tok; t += SC_PRODUCERS) {
-    float* At = A + t * DKP; float* Bt = B + t * DKP; float* Gt = Gd + t * DKP; float* Kt = KK + t * DKP;
-    if (MODE == 2) {
-      const float* ur = a.bonus + (size_t)h * dk;
-      float c = 0.f;
-      for (int i = lane; i < dk; i += 32) c = fmaf(Bt[i] * ur[i], Kt[i], c);
-      c = warp_sum(c);
-      if (lane == 0) { cc[t] = c; beta[t] = 1.f; }
-    } else {
-      float sq = 0.f, sk = 0.f, kq = 0.f;
-      for (int i = lane; i < DKP; i += 32) {
-        const float q = Bt[i], k = Kt[i];
-        sq = fmaf(q, q, sq); sk = fmaf(k, k, sk); kq = fmaf(k, q, kq);
-      }
-      sq = warp_sum(sq); sk = warp_sum(sk); kq = warp_sum(kq);
-      const float kn = 1.0f / sqrtf(sk + 1e-6f);
-      const float qn = 1.0f / (sqrtf(sq + 1e-6f) * sqrtf((float)dk));
+    for (int u = 0; u < TPW; ++u) { sq[u] = warp_sum(sq[u]); sk[u] = warp_sum(sk[u]); kq[u] = warp_sum(kq[u]); }
+#pragma unroll
+    for (int u = 0; u < TPW; ++u) {
+      const int t = pw + u * SC_PRODUCERS;
+      if (t >= n_tok) continue;
+      float* At = A + t * DKP; float* Bt = B + t * DKP; float* Gt = Gd + t * DKP; float* Kt = KK + t * DKP;
+      const float kn = 1.0f / sqrtf(sk[u] + 1e-6f);
+      const float qn = 1.0f / (sqrtf(sq[u] + 1e-6f) * sqrtf((float)dk));
       float gs = 0.f;
       if (MODE == 0) gs = expf(-rate * softplus_f(cc[t] + bias_a));
       for (int i = lane; i < DKP; i += 32) {
@@ -355,16 +400,18 @@ __device__ __forceinline__ void scan_stage(const ScanArgs& a, float* buf, int DK
         At[i] = gi * kk; Bt[i] = gi * qq; Gt[i] = gi; Kt[i] = kk;
       }
       __syncwarp();
-      if (lane == 0) { cc[t] = kq * kn * qn; beta[t] = sigmoid_f(beta[t]); }
+      if (lane == 0) { cc[t] = kq[u] * kn * qn; beta[t] = sigmoid_f(beta[t]); }
     }
   }
 }
 
-template <int MODE, int R4, typename TA>
+// KST: the lanes a column as a compile-time constant (0: read from the arguments).
+template <int MODE, int R4, int KST, typename TA>
 __global__ void __launch_bounds__(SC_THREADS) scan_kernel(ScanArgs a) {
   extern __shared__ __align__(16) float sc_smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int KS = a.KS, CPW = 32 / KS, COLS = SC_CONSUMERS * CPW, DKP = 4 * KS * R4;
+  const int KS = KST > 0 ? KST : a.KS;
+  const int CPW = 32 / KS, COLS = SC_CONSUMERS * CPW, DKP = 4 * KS * R4;
   const int col_tiles = (a.dv + COLS - 1) / COLS;
   const int h = blockIdx.x / col_tiles, col0 = (blockIdx.x - h * col_tiles) * COLS;
   const int item = blockIdx.y;
@@ -492,8 +539,13 @@ static int scan_launch(ScanArgs& a, int n_items, cudaStream_t stream) {
   a.tc = tc < 1 ? 1 : (tc > SC_MAX_TOK ? SC_MAX_TOK : tc);
   const size_t smem = (size_t)2 * a.tc * per_tok;
   dim3 grid(a.H * ((a.dv + COLS - 1) / COLS), n_items);
-  void (*kern)(ScanArgs) = R4 == 1 ? scan_kernel<MODE, 1, TA> : R4 == 2 ? scan_kernel<MODE, 2, TA>
-                         : R4 == 4 ? scan_kernel<MODE, 4, TA> : scan_kernel<MODE, 8, TA>;
+  void (*kern)(ScanArgs) = nullptr;
+#define SCAN_PICK(R4_, KS_) if (R4 == R4_ && KS == KS_) kern = scan_kernel<MODE, R4_, KS_, TA>
+  SCAN_PICK(1, 8); SCAN_PICK(2, 8); SCAN_PICK(4, 8); SCAN_PICK(1, 16); SCAN_PICK(2, 16); SCAN_PICK(4, 16);
+  SCAN_PICK(1, 32); SCAN_PICK(2, 32); SCAN_PICK(4, 32);
+#undef SCAN_PICK
+  if (!kern) kern = R4 == 1 ? scan_kernel<MODE, 1, 0, TA> : R4 == 2 ? scan_kernel<MODE, 2, 0, TA>
+                  : R4 == 4 ? scan_kernel<MODE, 4, 0, TA> : scan_kernel<MODE, 8, 0, TA>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;

@@ -87,31 +87,37 @@ class GatedDelta(Mixer):
             self.decls["g2.weight"] = ParamDecl((H * dv, -1), init=("normal", 0.2), fallback=(H * dv, R))
 
     def prepare(self):
+        """Every projection that reads the mixer's input is one product: [q; k; v; (g); b; a or a1; (g1)], stored in
+        float32 (the logits of beta and of the decay must not be rounded, and one launch is cheaper than two)."""
         w = self.w
         G, H, dk, dv = self.G, self.H, self.dk, self.dv
         self.n_conv = 2 * G * dk + H * dv
-        big = [w.pop("q.weight"), w.pop("k.weight"), w.pop("v.weight")]
+        mats = [w.pop("q.weight"), w.pop("k.weight"), w.pop("v.weight")]
+        names = ["q", "k", "v"]
         if self.gate == "silu":
-            big.append(w.pop("g.weight"))
-        w["big.weight"], offs = stack_rows(big)
-        self.k_off, self.v_off = offs[1], offs[2]
-        self.g_off = offs[3] if self.gate == "silu" else None
-        w["taps"] = torch.cat([w.pop("q.conv"), w.pop("k.conv"), w.pop("v.conv")], 0).contiguous()
-        small = [w.pop("b.weight")]
+            mats.append(w.pop("g.weight"))
+            names.append("g")
+        mats.append(w.pop("b.weight"))
+        names.append("b")
         if self.decay == "head":
-            small.append(w.pop("a.weight"))
+            mats.append(w.pop("a.weight"))
+            names.append("a")
         else:
             a1, a2 = w.pop("a1.weight"), w["a2.weight"]
             if a1.shape[0] != a2.shape[1]:
                 raise WeightError(f"gated_delta: the decay's factors have ranks {a1.shape[0]} and {a2.shape[1]}")
-            small.append(a1)
+            mats.append(a1)
+            names.append("a")
         if self.gate == "sigmoid_lowrank":
             g1, g2 = w.pop("g1.weight"), w["g2.weight"]
             if g1.shape[0] != g2.shape[1]:
                 raise WeightError(f"gated_delta: the gate's factors have ranks {g1.shape[0]} and {g2.shape[1]}")
-            small.append(g1)
-        self.small_rows = [m.shape[0] for m in small]
-        w["small.weight"], self.small_offs = stack_rows(small)
+            mats.append(g1)
+            names.append("g")
+        w["in.weight"], offs = stack_rows(mats)
+        self.off = dict(zip(names, offs))
+        self.rows = {n: m.shape[0] for n, m in zip(names, mats)}
+        w["taps"] = torch.cat([w.pop("q.conv"), w.pop("k.conv"), w.pop("v.conv")], 0).contiguous()
 
     def cache_need(self):
         return [FixedState((self.taps - 1, 2 * self.G * self.dk + self.H * self.dv)),
@@ -121,31 +127,28 @@ class GatedDelta(Mixer):
         if reads_only:
             raise ConfigError("a gated_delta layer cannot run on another layer's state")
         conv_state, mat_state = cache
-        w = self.w
+        w, off = self.w, self.off
         H, G, dk, dv = self.H, self.G, self.dk, self.dv
-        big = linear(xn, w["big.weight"])                                   # [T, q | k | v (| g)]
-        small = linear(xn, w["small.weight"], out_dtype=torch.float32)      # [T, b | a or a1 (| g1)] float32
-        qkv = ops.causal_conv_act(big[:, :self.n_conv], w["taps"], conv_state.states, ctx.item_start,
+        p = linear(xn, w["in.weight"], out_dtype=torch.float32)            # [T, q | k | v | (g) | b | a or a1 | (g1)] float32
+        qkv = ops.causal_conv_act(p[:, :self.n_conv], w["taps"], conv_state.states, ctx.item_start,
                                   conv_state.item_slot, ctx.n_items, ctx.max_item_rows, act="silu")
-        a_off = self.small_offs[1]
         gch = None
         if self.decay == "channel":
-            gch = ops.lowrank_expand(small[:, a_off:a_off + self.small_rows[1]], w["a2.weight"], w["dt_bias"],
+            gch = ops.lowrank_expand(p[:, off["a"]:off["a"] + self.rows["a"]], w["a2.weight"], w["dt_bias"],
                                      f_out="decay_softplus", rate=w["A_log"], per=dk)
-        o = ops.delta_scan(qkv, self.k_off, self.v_off, small, self.small_offs[0], a_off, w["A_log"],
+        o = ops.delta_scan(qkv, off["k"], off["v"], p, off["b"], off["a"], w["A_log"],
                            None if gch is not None else w["dt_bias"], gch, mat_state.states, ctx.item_start,
                            mat_state.item_slot, ctx.n_items, H, G, dk, dv)
         if self.gate == "silu":
-            gate, act = big[:, self.g_off:self.g_off + H * dv], "silu"
+            gate, act = p[:, off["g"]:off["g"] + H * dv], "silu"
         else:
-            g_off = self.small_offs[-1]
-            gate, act = ops.lowrank_expand(small[:, g_off:g_off + self.small_rows[-1]], w["g2.weight"]), "sigmoid"
+            gate, act = ops.lowrank_expand(p[:, off["g"]:off["g"] + self.rows["g"]], w["g2.weight"]), "sigmoid"
         y = ops.head_norm_gate(o, w["norm.weight"], False, gate, act, self.eps, H, dv, xn.dtype)
         linear(y, w["o.weight"], out=out, accumulate=True)
         return out
 
     def weight_order(self):
-        return [self.w["big.weight"], self.w["small.weight"], self.w["o.weight"]]
+        return [self.w["in.weight"], self.w["o.weight"]]
 
     def kernel_modules(self, dtype):
         return linear_modules(dtype) + [("recurrent", None)]

@@ -43,9 +43,9 @@ class ParallelBranches(Mixer):
         if reads_only:
             raise ConfigError("a parallel mixer cannot run on another layer's cache")
         outs = []
-        for p, (at, n, is_list) in zip(self.parts, self._spans):
+        bufs = torch.zeros((len(self.parts), xn.shape[0], self.size), dtype=torch.float32, device=out.device)   # one memset
+        for p, (at, n, is_list), buf in zip(self.parts, self._spans, bufs):
             view = cache[at:at + n] if is_list else (cache[at] if n else None)
-            buf = torch.zeros((xn.shape[0], self.size), dtype=torch.float32, device=out.device)
             p.forward(xn, ctx, view, buf)
             outs.append(buf)
         ops.branch_combine(out, outs, [self.w[f"out.{i}.weight"] for i in range(len(outs))], self.eps)
