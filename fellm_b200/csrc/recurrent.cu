@@ -423,14 +423,21 @@ __global__ void __launch_bounds__(SC_THREADS) scan_kernel(ScanArgs a) {
   const bool live = consumer && j < a.dv;
   float* Sg = a.state + (size_t)a.item_slot[item] * a.slot_stride + (size_t)h * a.dk * a.dv;
   float S[4 * R4];
+  // In memory a head's state is kept column by column (element (i, j) at j * dk + i): a thread's four rows are one
+  // 16-byte load and a warp's lanes read a column's rows side by side.  Nothing but this kernel reads the layout.
+  const bool s_vec = (a.dk & 3) == 0;
   if (consumer) {
 #pragma unroll
-    for (int r4 = 0; r4 < R4; ++r4)
+    for (int r4 = 0; r4 < R4; ++r4) {
+      const int i0 = 4 * (ks + KS * r4);
+      if (live && s_vec && i0 < a.dk) {
+        const float4 t = *(const float4*)(Sg + (size_t)j * a.dk + i0);
+        S[4 * r4] = t.x; S[4 * r4 + 1] = t.y; S[4 * r4 + 2] = t.z; S[4 * r4 + 3] = t.w;
+      } else {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        int i = 4 * (ks + KS * r4) + e;
-        S[4 * r4 + e] = (live && i < a.dk) ? Sg[(size_t)i * a.dv + j] : 0.f;
+        for (int e = 0; e < 4; ++e) S[4 * r4 + e] = (live && i0 + e < a.dk) ? Sg[(size_t)j * a.dk + i0 + e] : 0.f;
       }
+    }
   }
   const int n_stages = (n + a.tc - 1) / a.tc;
   if (!consumer) scan_stage<MODE, TA>(a, sc_smem, DKP, COLS, h, col0, row_begin, min(a.tc, n), (int)threadIdx.x - SC_CONSUMERS * 32);
@@ -504,17 +511,21 @@ __global__ void __launch_bounds__(SC_THREADS) scan_kernel(ScanArgs a) {
   }
   if (live) {
 #pragma unroll
-    for (int r4 = 0; r4 < R4; ++r4)
+    for (int r4 = 0; r4 < R4; ++r4) {
+      const int i0 = 4 * (ks + KS * r4);
+      if (s_vec && i0 < a.dk) {
+        *(float4*)(Sg + (size_t)j * a.dk + i0) = make_float4(S[4 * r4], S[4 * r4 + 1], S[4 * r4 + 2], S[4 * r4 + 3]);
+      } else {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        int i = 4 * (ks + KS * r4) + e;
-        if (i < a.dk) Sg[(size_t)i * a.dv + j] = S[4 * r4 + e];
+        for (int e = 0; e < 4; ++e)
+          if (i0 + e < a.dk) Sg[(size_t)j * a.dk + i0 + e] = S[4 * r4 + e];
       }
+    }
   }
 }
 
 template <int MODE, typename TA>
-static int scan_launch(ScanArgs& a, int n_items, cudaStream_t stream) {
+static int scan_launch(ScanArgs& a, int n_items, int max_item_rows, cudaStream_t stream) {
   int KS = 1;
   while (KS < 32 && a.dk > 16 * KS) KS <<= 1;                // up to 16 rows a thread while dk <= 512
   // more lanes a column while one item's blocks do not fill the device and a lane keeps four rows or more
@@ -537,6 +548,7 @@ static int scan_launch(ScanArgs& a, int n_items, cudaStream_t stream) {
   const int per_tok = (4 * DKP + COLS + 4) * (int)sizeof(float);
   int tc = 40960 / per_tok;
   a.tc = tc < 1 ? 1 : (tc > SC_MAX_TOK ? SC_MAX_TOK : tc);
+  if (max_item_rows > 0 && max_item_rows < a.tc) a.tc = max_item_rows;      // a decode step stages one token: 4 KB a block, not 67
   const size_t smem = (size_t)2 * a.tc * per_tok;
   dim3 grid(a.H * ((a.dv + COLS - 1) / COLS), n_items);
   void (*kern)(ScanArgs) = nullptr;
@@ -560,7 +572,7 @@ static int scan_launch(ScanArgs& a, int n_items, cudaStream_t stream) {
 FELLM_API int fellm_delta_scan(const void* qkv, int is_bf16, int ldq, int k_off, int v_off, const float* small, int lds,
                                int b_off, int a_off, const float* A_log, const float* dt_bias, const float* gch,
                                float* state, long long slot_stride, const int* item_start, const int* item_slot,
-                               float* out, int n_items, int H, int G, int dk, int dv, cudaStream_t stream) {
+                               float* out, int n_items, int H, int G, int dk, int dv, int max_item_rows, cudaStream_t stream) {
   if (n_items <= 0) return 0;
   if (dk < 1 || dk > 1024 || dv < 1 || G < 1 || H % G) return FELLM_ERR_SIZE;
   if (!qkv || !small || !state || !item_start || !item_slot || !out || (!gch && (!A_log || !dt_bias))) return FELLM_ERR_ARG;
@@ -568,21 +580,22 @@ FELLM_API int fellm_delta_scan(const void* qkv, int is_bf16, int ldq, int k_off,
   a.q = qkv; a.ld = ldq; a.k_off = k_off; a.v_off = v_off; a.small = small; a.lds = lds; a.b_off = b_off; a.a_off = a_off;
   a.A_log = A_log; a.dt_bias = dt_bias; a.gch = gch; a.state = state; a.slot_stride = slot_stride;
   a.item_start = item_start; a.item_slot = item_slot; a.out = out; a.H = H; a.G = G; a.dk = dk; a.dv = dv;
-  if (gch) return is_bf16 ? scan_launch<1, bf16>(a, n_items, stream) : scan_launch<1, float>(a, n_items, stream);
-  return is_bf16 ? scan_launch<0, bf16>(a, n_items, stream) : scan_launch<0, float>(a, n_items, stream);
+  if (gch) return is_bf16 ? scan_launch<1, bf16>(a, n_items, max_item_rows, stream) : scan_launch<1, float>(a, n_items, max_item_rows, stream);
+  return is_bf16 ? scan_launch<0, bf16>(a, n_items, max_item_rows, stream) : scan_launch<0, float>(a, n_items, max_item_rows, stream);
 }
 
 // Decay-and-bonus recurrence.  r, k, v [T, ld] (H x dk each), w float32 [T, H*dk] (the decay itself), u [H, dk].
 FELLM_API int fellm_decay_bonus_scan(const void* r, const void* k, const void* v, int is_bf16, int ld, const float* w,
                                      const float* u, float* state, long long slot_stride, const int* item_start,
-                                     const int* item_slot, float* out, int n_items, int H, int dk, cudaStream_t stream) {
+                                     const int* item_slot, float* out, int n_items, int H, int dk, int max_item_rows,
+                                     cudaStream_t stream) {
   if (n_items <= 0) return 0;
   if (dk < 1 || dk > 1024 || H < 1) return FELLM_ERR_SIZE;
   if (!r || !k || !v || !w || !u || !state || !item_start || !item_slot || !out) return FELLM_ERR_ARG;
   ScanArgs a = {};
   a.q = r; a.k = k; a.v = v; a.ld = ld; a.gch = w; a.bonus = u; a.state = state; a.slot_stride = slot_stride;
   a.item_start = item_start; a.item_slot = item_slot; a.out = out; a.H = H; a.G = H; a.dk = dk; a.dv = dk;
-  return is_bf16 ? scan_launch<2, bf16>(a, n_items, stream) : scan_launch<2, float>(a, n_items, stream);
+  return is_bf16 ? scan_launch<2, bf16>(a, n_items, max_item_rows, stream) : scan_launch<2, float>(a, n_items, max_item_rows, stream);
 }
 
 // ---------------------------------------------------------------- per-head norm and gate

@@ -383,11 +383,13 @@ def lowrank_expand(z, w2, bias=None, *, f_in="none", f_out="none", rate=None, pe
 
 
 def delta_scan(qkv, k_off, v_off, small, b_off, a_off, A_log, dt_bias, gch, state, item_start, item_slot, n_items,
-               H, G, dk, dv, out=None):
+               H, G, dk, dv, out=None, max_item_rows=0):
     """The gated delta rule over the step's portions.  qkv [T, *]: q (G x dk) at column 0, k at k_off, v (H x dv) at
     v_off, after convolution and SiLU; small float32 [T, *]: beta's logit at b_off + h and, for a decay per head,
     its logit at a_off + h (A_log, dt_bias [H]); gch float32 [T, H*dk]: the decay per head and key channel itself
-    (then A_log and dt_bias are not read).  state float32 [slots, H, dk, dv].  Returns o float32 [T, H*dv]."""
+    (then A_log and dt_bias are not read).  state float32 [slots, H, dk, dv] (the kernel's own: it keeps each
+    head's matrix column by column there).  Returns o float32 [T, H*dv].
+    max_item_rows: the longest portion of the step, if known (sizes the staging buffers; no result depends on it)."""
     _dev(qkv, small, A_log, dt_bias, gch, state, item_start, item_slot)
     T = qkv.shape[0]
     if dk > MAX_SCAN_KEY_DIM:
@@ -401,14 +403,15 @@ def delta_scan(qkv, k_off, v_off, small, b_off, a_off, A_log, dt_bias, gch, stat
     sp, ss = _state_args(state)
     f = _fn("recurrent", "fellm_delta_scan",
             [_c_p, _c_int, _c_int, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_ll, _c_p, _c_p,
-             _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p])
+             _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p])
     _check(f(_p(qkv), _is_bf16(qkv), qkv.stride(0), k_off, v_off, _p(small), small.stride(0), b_off, a_off, _p(A_log),
-             _p(dt_bias), _p(gch), sp, ss, _p(item_start), _p(item_slot), _p(out), n_items, H, G, dk, dv, _stream()),
+             _p(dt_bias), _p(gch), sp, ss, _p(item_start), _p(item_slot), _p(out), n_items, H, G, dk, dv,
+             int(max_item_rows), _stream()),
            "delta_scan")
     return out
 
 
-def decay_bonus_scan(r, k, v, w, u, state, item_start, item_slot, n_items, H, dk, out=None):
+def decay_bonus_scan(r, k, v, w, u, state, item_start, item_slot, n_items, H, dk, out=None, max_item_rows=0):
     """o_t = (S + diag(u) k_t v_t^T)^T r_t; S = diag(w_t) S + k_t v_t^T per head.  r, k, v [T, H*dk] (one row stride),
     w float32 [T, H*dk], u float32 [H, dk], state float32 [slots, H, dk, dk].  Returns o float32 [T, H*dk]."""
     _dev(r, k, v, w, u, state, item_start, item_slot)
@@ -422,9 +425,9 @@ def decay_bonus_scan(r, k, v, w, u, state, item_start, item_slot, n_items, H, dk
         out = torch.empty((T, H * dk), dtype=torch.float32, device=r.device)
     sp, ss = _state_args(state)
     f = _fn("recurrent", "fellm_decay_bonus_scan",
-            [_c_p, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p])
+            [_c_p, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_p])
     _check(f(_p(r), _p(k), _p(v), _is_bf16(r), r.stride(0), _p(w), _p(u), sp, ss, _p(item_start), _p(item_slot), _p(out),
-             n_items, H, dk, _stream()), "decay_bonus_scan")
+             n_items, H, dk, int(max_item_rows), _stream()), "decay_bonus_scan")
     return out
 
 

@@ -138,7 +138,7 @@ class GatedDelta(Mixer):
                                      f_out="decay_softplus", rate=w["A_log"], per=dk)
         o = ops.delta_scan(qkv, off["k"], off["v"], p, off["b"], off["a"], w["A_log"],
                            None if gch is not None else w["dt_bias"], gch, mat_state.states, ctx.item_start,
-                           mat_state.item_slot, ctx.n_items, H, G, dk, dv)
+                           mat_state.item_slot, ctx.n_items, H, G, dk, dv, max_item_rows=ctx.max_item_rows)
         if self.gate == "silu":
             gate, act = p[:, off["g"]:off["g"] + H * dv], "silu"
         else:

@@ -70,7 +70,7 @@ class TimeMix(Mixer):
         z = linear(mixes[4], w["w1.weight"], out_dtype=torch.float32)
         decay = ops.lowrank_expand(z[:, :self.rank], w["w2.weight"], w["w0"], f_in="tanh", f_out="exp_neg_exp")
         o = ops.decay_bonus_scan(r, k, v, decay, w["u"], mat_state.states, ctx.item_start, mat_state.item_slot,
-                                 ctx.n_items, self.H, self.dk)
+                                 ctx.n_items, self.H, self.dk, max_item_rows=ctx.max_item_rows)
         y = ops.head_norm_gate(o, w["norm.weight"], True, g, "silu", self.eps, self.H, self.dk, xn.dtype)
         linear(y, w["o.weight"], out=out, accumulate=True)
         return out
