@@ -61,7 +61,14 @@ CFG_S = dict(architecture="Robazen", vocab=101, width=72, norm=dict(eps=1e-5), l
     layer("channel_delta", delta(6, 2, 10, 3, 5), ff=24),
 ], loop=dict(start=2, stop=3, times=1))
 
-CONFIGS = {"P": (CFG_P, 11), "Q": (CFG_Q, 12), "R": (CFG_R, 13), "S": (CFG_S, 14)}
+# W: not tiny in width: the sizes at which a decode step's products take the norm in, and the attention of portions
+# runs on tensor cores (keys and values of one size)
+CFG_W = dict(architecture="Robazen", vocab=256, width=1024, norm=dict(eps=1e-5), layers=[
+    layer("delta", delta(8, 4, 64, 128, 4), ff=2048),
+    layer("parallel", parallel(16, 8, 64, 64, 32, 0.11, 30.0, 16, 64), ff=2048),
+])
+
+CONFIGS = {"P": (CFG_P, 11), "Q": (CFG_Q, 12), "R": (CFG_R, 13), "S": (CFG_S, 14), "W": (CFG_W, 15)}
 _tmp = tempfile.TemporaryDirectory(prefix="fellm_b200_robazen_")
 
 

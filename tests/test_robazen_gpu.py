@@ -461,6 +461,15 @@ def test_unequal_batch_against_each_alone_with_slots_and_pages_that_come_again(e
         assert d < U.LIMIT[engines.dtype], (i, d)
 
 
+def test_wide_model(engines):
+    """Width 1,024, heads of 64 and 128, pages of 64 tokens: the sizes at which the products run on their tensor-core
+    kernels and the attention of portions on its own; portions, then token by token."""
+    name, T = "W", 44
+    toks = U.tokens(name, T, 7)
+    got = U.run_cuts(engines(name, page_tokens=64), "a", toks, [30, 2, 5])
+    assert U.distance(got, U.plain_logits(name, T, 7)) < U.LIMIT[engines.dtype]
+
+
 def test_long_decoding(engines):
     name, T = "R", 420
     toks = U.tokens(name, T, 5)
