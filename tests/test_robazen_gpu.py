@@ -405,8 +405,10 @@ def test_prompt_against_token_by_token(engines, name):
     toks = U.tokens(name, T, 2)
     whole = U.run_cuts(eng, "a", toks, [T])
     single = U.run_cuts(eng, "b", toks, [])
-    lim = 1e-5 if engines.dtype == "float32" else U.LIMIT["bfloat16"]
-    assert U.distance(single, whole) < lim
+    if engines.dtype == "float32":
+        # every sum's order is set by the model's sizes, not by the cut: the 32-bit engine repeats itself bit for bit
+        assert torch.equal(single, whole)
+    assert U.distance(single, whole) < U.LIMIT["bfloat16"]
     assert U.distance(single, U.plain_logits(name, T, 2)) < U.LIMIT[engines.dtype]
 
 
