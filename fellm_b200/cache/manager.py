@@ -76,7 +76,7 @@ class SlotAllocator(PageAllocator):
 @dataclass
 class PagedView:
     """What an attention mixer sees of its cache."""
-    pool: torch.Tensor            # [pages, layers, 2, G, page_tokens, hd]
+    pool: torch.Tensor            # [pages, layers, 2, G, page_tokens, hd]; [pages, layers, record] where values differ from keys in size or are the keys
     block_table: torch.Tensor     # [slots, width] int32 on the device
     layer: int                    # index in the group
     page_tokens: int

@@ -14,8 +14,11 @@
 // Beyond FeLLM's attention the kernel takes: values of another size than keys (vd; a page-layer record is
 // K [G][tokens][hd] followed by V [G][tokens][vd]), queries read in place from a wider row (ldq), a soft cap on
 // the scores (cap * tanh(s / cap)), blocks of `chunk` positions that a query does not look out of, and a gate
-// per (row, head) whose sigmoid scales the head's output.  kv_write puts a step's keys and values, as the
-// product left them, into their pages.
+// per (row, head) whose sigmoid scales the head's output; a bias by distance, slope[h] * (query position - key
+// position) taken off the scaled score; a query temperature by position, q times
+// 1 + coef * ln(floor((p + 1) / every) + 1); and values that ARE the keys (vd == 0 in the record: a page-layer
+// record then holds the keys alone and the read-out has the keys' size).  kv_write puts a step's keys and values,
+// as the product left them, into their pages.
 #include "common.cuh"
 
 #define MAX_HD 256
@@ -27,7 +30,8 @@ paged_attention_simt_kernel(const TA* __restrict__ q, const TC* __restrict__ poo
                             const int* __restrict__ positions, const int* __restrict__ row_slot,
                             TA* __restrict__ out, int T, int H, int G, int hd, int page_tokens, int layer,
                             int layers_in_group, float scale, int window, int vd, int ldq, float softcap, int chunk,
-                            const float* __restrict__ gate, int ldg) {
+                            const float* __restrict__ gate, int ldg, const float* __restrict__ slopes,
+                            float qt_coef, int qt_every) {
   FELLM_TRACE_SCOPE(TRACE_ATTENTION_SIMT);
   extern __shared__ float qs_all[];                 // [warps per block][hd]
   int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -37,13 +41,17 @@ paged_attention_simt_kernel(const TA* __restrict__ q, const TC* __restrict__ poo
   int g = h / (H / G);
   float* qs = qs_all + (size_t)wib * hd;
   const TA* qr = q + (size_t)row * ldq + (size_t)h * hd;
-  for (int e = lane; e < hd; e += 32) qs[e] = to_f(qr[e]);
-  __syncwarp();
   int pos = positions[row];
+  const float qt = qt_every > 0 ? 1.0f + qt_coef * logf((float)((pos + 1) / qt_every + 1)) : 1.0f;
+  for (int e = lane; e < hd; e += 32) qs[e] = to_f(qr[e]) * qt;
+  __syncwarp();
+  const float slope = slopes ? slopes[h] : 0.f;
+  const bool v_is_k = vd == 0;          // the values are the keys: nothing else is stored
+  if (v_is_k) vd = hd;
   const int* bt = block_table + (size_t)row_slot[row] * max_pages;
   int k_begin = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
   if (chunk > 0) k_begin = max(k_begin, (pos / chunk) * chunk);
-  const size_t record = (size_t)G * page_tokens * (hd + vd);       // one page of one layer: keys, then values
+  const size_t record = (size_t)G * page_tokens * (v_is_k ? hd : hd + vd);       // one page of one layer: keys, then values
 
   float m = -INFINITY, l = 0.f;
   float acc[MAX_HD / 32];
@@ -59,11 +67,12 @@ paged_attention_simt_kernel(const TA* __restrict__ q, const TC* __restrict__ poo
       const TC* rec = pool + ((size_t)page * layers_in_group + layer) * record;
       size_t tok = (size_t)g * page_tokens + (kj % page_tokens);
       const TC* krow = rec + tok * hd;
-      vrow = rec + (size_t)G * page_tokens * hd + tok * vd;
+      vrow = v_is_k ? krow : rec + (size_t)G * page_tokens * hd + tok * vd;
       float dot = 0.f;
       for (int e = 0; e < hd; ++e) dot = fmaf(qs[e], to_f(krow[e]), dot);
       s = dot * scale;
       if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+      s -= slope * (float)(pos - kj);
     }
     float m_new = fmaxf(m, warp_max(s));
     float p = kj <= pos ? expf(s - m_new) : 0.f;
@@ -144,9 +153,10 @@ FELLM_API int fellm_paged_attention_general(const void* q, int act_bf16, const v
                                             const int* row_slot, void* out, int T, int H, int G, int hd,
                                             int page_tokens, int layer, int layers_in_group, float scale,
                                             int window, int vd, int ldq, float softcap, int chunk, const float* gate,
-                                            int ldg, cudaStream_t stream) {
+                                            int ldg, const float* slopes, float qt_coef, int qt_every,
+                                            cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (hd < 1 || hd > MAX_HD || vd < 1 || vd > MAX_HD) return FELLM_ERR_SIZE;
+  if (hd < 1 || hd > MAX_HD || vd < 0 || vd > MAX_HD) return FELLM_ERR_SIZE;
   if (G < 1 || H % G) return FELLM_ERR_SIZE;
   if (!q || !pool || !block_table || !positions || !row_slot || !out) return FELLM_ERR_ARG;
   if (act_bf16 != cache_bf16) return FELLM_ERR_ARG;
@@ -157,11 +167,11 @@ FELLM_API int fellm_paged_attention_general(const void* q, int act_bf16, const v
   if (act_bf16)
     paged_attention_simt_kernel<bf16, bf16><<<blocks, warps_per_block * 32, smem, stream>>>((const bf16*)q,
         (const bf16*)pool, block_table, max_pages, positions, row_slot, (bf16*)out, T, H, G, hd, page_tokens,
-        layer, layers_in_group, scale, window, vd, ldq, softcap, chunk, gate, ldg);
+        layer, layers_in_group, scale, window, vd, ldq, softcap, chunk, gate, ldg, slopes, qt_coef, qt_every);
   else
     paged_attention_simt_kernel<float, float><<<blocks, warps_per_block * 32, smem, stream>>>((const float*)q,
         (const float*)pool, block_table, max_pages, positions, row_slot, (float*)out, T, H, G, hd, page_tokens,
-        layer, layers_in_group, scale, window, vd, ldq, softcap, chunk, gate, ldg);
+        layer, layers_in_group, scale, window, vd, ldq, softcap, chunk, gate, ldg, slopes, qt_coef, qt_every);
   return launch_status();
 }
 
@@ -172,5 +182,5 @@ FELLM_API int fellm_paged_attention_simt(const void* q, int act_bf16, const void
                                          int window, cudaStream_t stream) {
   return fellm_paged_attention_general(q, act_bf16, pool, cache_bf16, block_table, max_pages, positions, row_slot, out,
                                        T, H, G, hd, page_tokens, layer, layers_in_group, scale, window, hd, H * hd, 0.f,
-                                       0, nullptr, 0, stream);
+                                       0, nullptr, 0, nullptr, 0.f, 0, stream);
 }

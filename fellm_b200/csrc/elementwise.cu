@@ -1,4 +1,5 @@
-// Embedding gather, RMSNorm, SiLU-gate, row gather.
+// Embedding gather (times a constant), RMSNorm, SiLU-gate, row gather, a vector added to every row, scaled and
+// soft-capped logits.
 //
 // FeLLM counterparts (plugins/cuda_kernels/src/oxide_kernels.rs): embedding_bf16_rows (3140),
 // rmsnorm_group (165), silu_gate (67).  The residual stream is float32 in both engine dtypes;
@@ -8,7 +9,7 @@
 // ---------------------------------------------------------------- embedding
 template <typename TW>
 __global__ void embed_rows_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
-                                  float* __restrict__ out, int d, int vocab, int* __restrict__ status) {
+                                  float* __restrict__ out, int d, int vocab, int* __restrict__ status, float scale) {
   FELLM_TRACE_SCOPE(TRACE_EMBED_ROWS);
   pdl_launch_dependents();
   pdl_wait(); FELLM_TRACE_WAITED();                 // the residual buffer may still be read by the step before
@@ -21,17 +22,17 @@ __global__ void embed_rows_kernel(const int* __restrict__ tokens, const TW* __re
     return;
   }
   const TW* src = table + (size_t)tok * d;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_f(src[i]);
+  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_f(src[i]) * scale;
 }
 
 FELLM_API int fellm_embed_rows(const int* tokens, const void* table, int table_is_bf16, float* out,
-                               int rows, int d, int vocab, int* status, cudaStream_t stream) {
+                               int rows, int d, int vocab, int* status, float scale, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (!tokens || !table || !out) return FELLM_ERR_ARG;
   int threads = d >= 256 ? 256 : (d >= 128 ? 128 : 64);
   if (table_is_bf16)
-    return launch_k_class(launch_class_for_rows(rows, 2), embed_rows_kernel<bf16>, dim3(rows), dim3(threads), 0, stream, 1, tokens, (const bf16*)table, out, d, vocab, status);
-  return launch_k_class(launch_class_for_rows(rows, 2), embed_rows_kernel<float>, dim3(rows), dim3(threads), 0, stream, 1, tokens, (const float*)table, out, d, vocab, status);
+    return launch_k_class(launch_class_for_rows(rows, 2), embed_rows_kernel<bf16>, dim3(rows), dim3(threads), 0, stream, 1, tokens, (const bf16*)table, out, d, vocab, status, scale);
+  return launch_k_class(launch_class_for_rows(rows, 2), embed_rows_kernel<float>, dim3(rows), dim3(threads), 0, stream, 1, tokens, (const float*)table, out, d, vocab, status, scale);
 }
 
 // ---------------------------------------------------------------- RMSNorm
@@ -222,4 +223,35 @@ FELLM_API int fellm_concat_cast(const float* a, const float* b, void* out, int o
   int blocks = (int)((n + 255) / 256); if (blocks > fellm_sm_count() * 16) blocks = fellm_sm_count() * 16;
   if (out_is_bf16) return launch_k_class(launch_class_for_rows(rows, 0), concat_cast_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, 1, a, b, (bf16*)out, rows, d);
   return launch_k_class(launch_class_for_rows(rows, 0), concat_cast_kernel<float>, dim3(blocks), dim3(256), 0, stream, 1, a, b, (float*)out, rows, d);
+}
+
+// ---------------------------------------------------------------- a vector added to every row
+// x[t, :] += v   (float32; what opens a pass of a looped run of layers)
+__global__ void add_row_vector_kernel(float* __restrict__ x, const float* __restrict__ v, long long n, int d) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) x[i] += v[i % d];
+}
+
+FELLM_API int fellm_add_row_vector(float* x, const float* v, int rows, int d, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (!x || !v || d < 1) return FELLM_ERR_ARG;
+  long long n = (long long)rows * d;
+  add_row_vector_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(x, v, n, d);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- logits: scale, then soft cap
+// z <- cap * tanh(z * scale / cap)   (cap <= 0: z <- z * scale), float32 in place
+__global__ void scale_softcap_kernel(float* __restrict__ z, long long n, float scale, float cap) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float v = z[i] * scale;
+  z[i] = cap > 0.f ? cap * tanhf(v / cap) : v;
+}
+
+FELLM_API int fellm_scale_softcap(float* z, long long n, float scale, float cap, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (!z) return FELLM_ERR_ARG;
+  scale_softcap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(z, n, scale, cap);
+  return launch_status();
 }

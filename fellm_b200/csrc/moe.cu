@@ -1,0 +1,377 @@
+// Routed experts (a mixture of small gated feed-forwards): everything between the router's logits and the sum
+// that goes into the residual stream, without a word to the host.
+//
+//   moe_route     softmax over the experts in float32, the `top` largest per token (ties: the lower expert), their
+//                 scores as they are (or renormalised to sum 1)
+//   moe_plan      (three kernels) the (token, choice) pairs sorted by expert: a count per tile of pairs and expert,
+//                 an exclusive scan in the order (expert, tile), each pair's place; and the table of row tiles
+//                 (expert, first row, rows) that the grouped products walk
+//   moe_gemm      grouped product over the table: C[r, :] = A[row(r), :] W[e]^T, with the input rows gathered by
+//                 token (first product, SiLU(gate) * up in the epilogue) or taken in sorted order (second product)
+//   moe_combine   x[t, :] += sum_c score[t, c] * y[place(t, c), :], c in order
+//
+// A row's arithmetic depends on the row alone: a pair's place among its expert's rows moves it inside a tile, never
+// into another sum; every sum over K runs in the order of K; the sum over a token's experts runs in the order of the
+// choices.  So a token's result does not depend on the batch, and no atomics touch data.
+#include "common.cuh"
+
+#define MOE_MAX_TOP 16
+#define PLAN_TILE 1024
+
+// ---------------------------------------------------------------- routing
+// One warp per token.  logits float32 [T, ld]; idx [T, top] int32; w [T, top] float32.
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ logits, int ld, int T, int E, int top, int renorm,
+                 int* __restrict__ idx, float* __restrict__ w) {
+  const int warp = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (warp >= T) return;
+  const float* z = logits + (size_t)warp * ld;
+  float m = -INFINITY;
+  for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
+  m = warp_max(m);
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) sum += expf(z[e] - m);
+  sum = warp_sum(sum);
+  int taken[MOE_MAX_TOP];
+  float tw[MOE_MAX_TOP];
+  float chosen = 0.f;
+#pragma unroll
+  for (int c = 0; c < MOE_MAX_TOP; ++c) {
+    if (c >= top) break;
+    float best = -INFINITY; int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      bool free_ = true;
+#pragma unroll
+      for (int p = 0; p < MOE_MAX_TOP; ++p) if (p < c && taken[p] == e) free_ = false;
+      const float v = z[e];
+      if (free_ && (v > best || (v == best && e < bi))) { best = v; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    taken[c] = bi;
+    tw[c] = expf(best - m) / sum;
+    chosen += tw[c];
+  }
+  if (lane == 0) {
+#pragma unroll
+    for (int c = 0; c < MOE_MAX_TOP; ++c) {
+      if (c >= top) break;
+      idx[(size_t)warp * top + c] = taken[c];
+      w[(size_t)warp * top + c] = renorm ? tw[c] / chosen : tw[c];
+    }
+  }
+}
+
+FELLM_API int fellm_moe_route(const float* logits, int ld, int T, int E, int top, int renorm, int* idx, float* w,
+                              cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (E < 1 || top < 1 || top > E || top > MOE_MAX_TOP) return FELLM_ERR_SIZE;
+  if (!logits || !idx || !w) return FELLM_ERR_ARG;
+  moe_route_kernel<<<(T + 3) / 4, 128, 0, stream>>>(logits, ld, T, E, top, renorm, idx, w);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- the plan
+// Pairs p = t * top + c, P of them.  Tile i of PLAN_TILE pairs: counts[i][e] and each pair's rank among the pairs of
+// its tile that chose the same expert before it.
+__global__ void __launch_bounds__(PLAN_TILE)
+moe_count_kernel(const int* __restrict__ idx, int P, int E, int* __restrict__ counts, int* __restrict__ rank) {
+  __shared__ int ex[PLAN_TILE];
+  const int p = blockIdx.x * PLAN_TILE + threadIdx.x;
+  const int e = p < P ? idx[p] : -1;
+  ex[threadIdx.x] = e;
+  for (int i = threadIdx.x; i < E; i += PLAN_TILE) counts[(size_t)blockIdx.x * E + i] = 0;
+  __syncthreads();
+  if (e < 0) return;
+  int r = 0;
+  for (int j = 0; j < (int)threadIdx.x; ++j) r += ex[j] == e;
+  rank[p] = r;
+  // the last pair of its expert in the tile knows the count
+  bool last = true;
+  for (int j = threadIdx.x + 1; j < PLAN_TILE && last; ++j) last = ex[j] != e;
+  if (last) counts[(size_t)blockIdx.x * E + e] = r + 1;
+}
+
+// One block.  base[i][e] = first sorted row of tile i's pairs of expert e (experts in order, tiles in order inside an
+// expert); row tiles of BM rows: table[n] = (expert, first row, rows), n_tiles.
+__global__ void __launch_bounds__(1024)
+moe_scan_kernel(const int* __restrict__ counts, int n_plan_tiles, int E, int BM, int* __restrict__ base,
+                int* __restrict__ table, int* __restrict__ n_tiles) {
+  extern __shared__ int sh[];            // [E] rows of an expert, then [E] its first row, then [E] its first row tile
+  int* rows = sh; int* first = sh + E; int* first_tile = sh + 2 * E;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int n = 0;
+    for (int i = 0; i < n_plan_tiles; ++i) n += counts[(size_t)i * E + e];
+    rows[e] = n;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) { first[e] = at; first_tile[e] = tiles; at += rows[e]; tiles += (rows[e] + BM - 1) / BM; }
+    *n_tiles = tiles;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int at = first[e];
+    for (int i = 0; i < n_plan_tiles; ++i) { base[(size_t)i * E + e] = at; at += counts[(size_t)i * E + e]; }
+    int n = first_tile[e];
+    for (int r = 0; r < rows[e]; r += BM, ++n) {
+      table[3 * n] = e; table[3 * n + 1] = first[e] + r; table[3 * n + 2] = min(BM, rows[e] - r);
+    }
+  }
+}
+
+// sorted[place] = pair, place_of[pair] = place
+__global__ void moe_place_kernel(const int* __restrict__ idx, const int* __restrict__ rank, const int* __restrict__ base,
+                                 int P, int E, int* __restrict__ sorted, int* __restrict__ place_of) {
+  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= P) return;
+  const int place = base[(size_t)(p / PLAN_TILE) * E + idx[p]] + rank[p];
+  sorted[place] = p;
+  place_of[p] = place;
+}
+
+// scratch (int32): counts [tiles][E] | base [tiles][E] | rank [P]
+FELLM_API int fellm_moe_plan(const int* idx, int P, int E, int BM, int* scratch, int* sorted, int* place_of, int* table,
+                             int* n_tiles, cudaStream_t stream) {
+  if (P <= 0) return 0;
+  if (E < 1 || BM < 1) return FELLM_ERR_SIZE;
+  if (!idx || !scratch || !sorted || !place_of || !table || !n_tiles) return FELLM_ERR_ARG;
+  const int tiles = (P + PLAN_TILE - 1) / PLAN_TILE;
+  int* counts = scratch; int* base = counts + (size_t)tiles * E; int* rank = base + (size_t)tiles * E;
+  moe_count_kernel<<<tiles, PLAN_TILE, 0, stream>>>(idx, P, E, counts, rank);
+  const size_t sh = (size_t)3 * E * sizeof(int);
+  if (sh > 48 * 1024) return FELLM_ERR_SIZE;
+  moe_scan_kernel<<<1, 1024, sh, stream>>>(counts, tiles, E, BM, base, table, n_tiles);
+  moe_place_kernel<<<(P + 255) / 256, 256, 0, stream>>>(idx, rank, base, P, E, sorted, place_of);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- grouped products, float32 FMA
+// Every output is ONE chain of fused multiply-adds over k = 0..K-1: the 32-bit engine's product, and the bfloat16
+// engine's where the tensor-core kernel below does not take a size.
+// GATED: W[e] is [2N, K], gate rows first; the epilogue stores SiLU(gate) * up.  Rows of A: gather[row] / top when
+// gather is given (a pair's token), else the sorted row itself.
+#define FB 64
+#define FK 16
+template <typename TA, typename TW, typename TO, bool GATED>
+__global__ void __launch_bounds__(256)
+moe_gemm_fma_kernel(const TA* __restrict__ A, int lda, const int* __restrict__ gather, int top,
+                    const TW* __restrict__ W, TO* __restrict__ C, int ldc, int N, int K,
+                    const int* __restrict__ table, const int* __restrict__ n_tiles) {
+  if ((int)blockIdx.x >= *n_tiles) return;
+  __shared__ float As[FK][FB + 1];
+  __shared__ float Ws[GATED ? 2 : 1][FK][FB + 1];
+  __shared__ int arow[FB];
+  const int e = table[3 * blockIdx.x], row0 = table[3 * blockIdx.x + 1], rows = table[3 * blockIdx.x + 2];
+  const int n0 = blockIdx.y * FB;
+  const TW* We = W + (size_t)e * (GATED ? 2 : 1) * N * K;
+  for (int r = threadIdx.x; r < FB; r += 256)
+    arow[r] = r < rows ? (gather ? gather[row0 + r] / top : row0 + r) : -1;
+  __syncthreads();
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;       // 4 columns x 4 rows a thread
+  float acc[4][4], acc2[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = acc2[i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += FK) {
+    for (int i = threadIdx.x; i < FB * FK; i += 256) {
+      const int r = i / FK, k = i - r * FK;
+      const int ar = arow[r];
+      As[k][r] = (ar >= 0 && k0 + k < K) ? to_f(A[(size_t)ar * lda + k0 + k]) : 0.f;
+      const int n = n0 + r;
+      const bool ok = n < N && k0 + k < K;
+      Ws[0][k][r] = ok ? to_f(We[(size_t)n * K + k0 + k]) : 0.f;
+      if (GATED) Ws[1][k][r] = ok ? to_f(We[(size_t)(N + n) * K + k0 + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < FK; ++k) {
+      float a[4], b[4], b2[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[k][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { b[j] = Ws[0][k][tx * 4 + j]; if (GATED) b2[j] = Ws[1][k][tx * 4 + j]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+          if (GATED) acc2[i][j] = fmaf(a[i], b2[j], acc2[i][j]);
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = ty * 4 + i;
+    if (r >= rows) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= N) continue;
+      float v = acc[i][j];
+      if (GATED) {
+        // in the bfloat16 engine gate and up are activations like those of the dense feed-forward: rounded first
+        float g = to_f(from_f<TA>(v)), u = to_f(from_f<TA>(acc2[i][j]));
+        v = g / (1.0f + expf(-g)) * u;
+      }
+      C[(size_t)(row0 + r) * ldc + n] = from_f<TO>(v);
+    }
+  }
+}
+
+// ---------------------------------------------------------------- grouped products, bfloat16 tensor cores
+// 64 rows x 64 columns a CTA (x 2 column sets when GATED), K in steps of 32 through shared memory (rows padded to 40
+// elements: the fragment loads of a warp fall on different banks), four warps of 16 rows each, mma.m16n8k16 with
+// float32 accumulators.  A token's sum over K is the same chain of MMAs wherever the row lies in its tile.
+#define TB 64
+#define TK 32
+#define TLD 40
+__device__ __forceinline__ void mma16816(float* d, const unsigned* a, const unsigned* b) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+template <typename TO, bool GATED>
+__global__ void __launch_bounds__(128)
+moe_gemm_mma_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__ gather, int top,
+                    const bf16* __restrict__ W, TO* __restrict__ C, int ldc, int N, int K,
+                    const int* __restrict__ table, const int* __restrict__ n_tiles) {
+  if ((int)blockIdx.x >= *n_tiles) return;
+  __shared__ __align__(16) bf16 As[2][TB * TLD];
+  __shared__ __align__(16) bf16 Ws[2][(GATED ? 2 : 1) * TB * TLD];
+  __shared__ int arow[TB];
+  const int e = table[3 * blockIdx.x], row0 = table[3 * blockIdx.x + 1], rows = table[3 * blockIdx.x + 2];
+  const int n0 = blockIdx.y * TB;
+  const bf16* We = W + (size_t)e * (GATED ? 2 : 1) * N * K;
+  for (int r = threadIdx.x; r < TB; r += 128)
+    arow[r] = r < rows ? (gather ? gather[row0 + r] / top : row0 + r) : -1;
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+  constexpr int NB = GATED ? 16 : 8;                   // blocks of 8 columns a warp: 64 columns (and 64 of the up set)
+  float acc[NB][4];
+#pragma unroll
+  for (int j = 0; j < NB; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  // a thread copies 16 bytes at a time: 64 rows x 4 vectors of A, and of each column set of W
+  auto stage = [&](int buf, int k0) {
+    for (int i = threadIdx.x; i < TB * 4; i += 128) {
+      const int r = i >> 2, kv = (i & 3) * 8;
+      uint4 va = make_uint4(0, 0, 0, 0), vw = make_uint4(0, 0, 0, 0), vw2 = make_uint4(0, 0, 0, 0);
+      const int ar = arow[r];
+      if (ar >= 0 && k0 + kv < K) va = *(const uint4*)(A + (size_t)ar * lda + k0 + kv);
+      const int n = n0 + r;
+      if (n < N && k0 + kv < K) {
+        vw = *(const uint4*)(We + (size_t)n * K + k0 + kv);
+        if (GATED) vw2 = *(const uint4*)(We + (size_t)(N + n) * K + k0 + kv);
+      }
+      *(uint4*)(&As[buf][r * TLD + kv]) = va;
+      *(uint4*)(&Ws[buf][r * TLD + kv]) = vw;
+      if (GATED) *(uint4*)(&Ws[buf][(TB + r) * TLD + kv]) = vw2;
+    }
+  };
+  const int n_k = (K + TK - 1) / TK;
+  stage(0, 0);
+  __syncthreads();
+  for (int kb = 0; kb < n_k; ++kb) {
+    const int buf = kb & 1;
+    if (kb + 1 < n_k) stage(buf ^ 1, (kb + 1) * TK);
+    const bf16* as = As[buf] + (warp * 16) * TLD;
+#pragma unroll
+    for (int kk = 0; kk < TK; kk += 16) {
+      unsigned a[4];
+      a[0] = *(const unsigned*)(as + gid * TLD + kk + tig * 2);
+      a[1] = *(const unsigned*)(as + (gid + 8) * TLD + kk + tig * 2);
+      a[2] = *(const unsigned*)(as + gid * TLD + kk + 8 + tig * 2);
+      a[3] = *(const unsigned*)(as + (gid + 8) * TLD + kk + 8 + tig * 2);
+#pragma unroll
+      for (int j = 0; j < NB; ++j) {
+        const bf16* ws = Ws[buf] + (j * 8 + gid) * TLD + kk + tig * 2;
+        unsigned b[2];
+        b[0] = *(const unsigned*)ws;
+        b[1] = *(const unsigned*)(ws + 8);
+        mma16816(acc[j], a, b);
+      }
+    }
+    __syncthreads();
+  }
+  // c0, c1: row gid, columns 2 tig, 2 tig + 1; c2, c3: row gid + 8
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int r = warp * 16 + gid + half * 8;
+    if (r >= rows) continue;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int n = n0 + j * 8 + tig * 2 + c;
+        if (n >= N) continue;
+        float v = acc[j][half * 2 + c];
+        if (GATED) {
+          const float g = to_f(from_f<bf16>(v)), u = to_f(from_f<bf16>(acc[8 + j][half * 2 + c]));
+          v = g / (1.0f + expf(-g)) * u;
+        }
+        C[(size_t)(row0 + r) * ldc + n] = from_f<TO>(v);
+      }
+    }
+  }
+}
+
+// A [*, lda] (bfloat16 or float32), W [E][(gated ? 2 : 1) * N][K] of the same kind; C [P, ldc]: bfloat16 or float32
+// when gated (the activation), float32 otherwise.  max_tiles: the table's capacity = the launch's first extent.
+FELLM_API int fellm_moe_gemm(const void* A, int a_bf16, int lda, const int* gather, int top, const void* W, int w_bf16,
+                             void* C, int c_bf16, int ldc, int N, int K, int gated, const int* table, const int* n_tiles,
+                             int max_tiles, int use_mma, cudaStream_t stream) {
+  if (max_tiles <= 0) return 0;
+  if (N < 1 || K < 1 || top < 1) return FELLM_ERR_SIZE;
+  if (!A || !W || !C || !table || !n_tiles) return FELLM_ERR_ARG;
+  if (a_bf16 != w_bf16 || (!gated && c_bf16) || (gated && c_bf16 != a_bf16)) return FELLM_ERR_ARG;
+  const bool mma = use_mma && a_bf16 && K % 8 == 0 && lda % 8 == 0 && ((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0;
+  if (mma) {
+    dim3 grid(max_tiles, (N + TB - 1) / TB);
+    if (gated)
+      moe_gemm_mma_kernel<bf16, true><<<grid, 128, 0, stream>>>((const bf16*)A, lda, gather, top, (const bf16*)W, (bf16*)C, ldc, N, K, table, n_tiles);
+    else
+      moe_gemm_mma_kernel<float, false><<<grid, 128, 0, stream>>>((const bf16*)A, lda, gather, top, (const bf16*)W, (float*)C, ldc, N, K, table, n_tiles);
+    return launch_status();
+  }
+  dim3 grid(max_tiles, (N + FB - 1) / FB);
+  if (a_bf16) {
+    if (gated)
+      moe_gemm_fma_kernel<bf16, bf16, bf16, true><<<grid, 256, 0, stream>>>((const bf16*)A, lda, gather, top, (const bf16*)W, (bf16*)C, ldc, N, K, table, n_tiles);
+    else
+      moe_gemm_fma_kernel<bf16, bf16, float, false><<<grid, 256, 0, stream>>>((const bf16*)A, lda, gather, top, (const bf16*)W, (float*)C, ldc, N, K, table, n_tiles);
+  } else {
+    if (gated)
+      moe_gemm_fma_kernel<float, float, float, true><<<grid, 256, 0, stream>>>((const float*)A, lda, gather, top, (const float*)W, (float*)C, ldc, N, K, table, n_tiles);
+    else
+      moe_gemm_fma_kernel<float, float, float, false><<<grid, 256, 0, stream>>>((const float*)A, lda, gather, top, (const float*)W, (float*)C, ldc, N, K, table, n_tiles);
+  }
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- the weighted sum into the residual stream
+// x[t, :] += sum_c w[t, c] * y[place_of[t * top + c], :], c = 0 .. top-1 in order, float32.
+__global__ void moe_combine_kernel(float* __restrict__ x, const float* __restrict__ y, const int* __restrict__ place_of,
+                                   const float* __restrict__ w, int top, int d) {
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float s = 0.f;
+    for (int c = 0; c < top; ++c) s = fmaf(w[(size_t)t * top + c], y[(size_t)place_of[(size_t)t * top + c] * d + i], s);
+    x[(size_t)t * d + i] += s;
+  }
+}
+
+FELLM_API int fellm_moe_combine(float* x, const float* y, const int* place_of, const float* w, int T, int top, int d,
+                                cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (!x || !y || !place_of || !w) return FELLM_ERR_ARG;
+  moe_combine_kernel<<<T, d >= 256 ? 256 : 128, 0, stream>>>(x, y, place_of, w, top, d);
+  return launch_status();
+}

@@ -5,6 +5,7 @@
 //   lowrank_expand     out = f_out(W2 f_in(z) + bias): the second factor of a low-rank projection, float32
 //   delta_scan         gated delta rule:  S = g S; u = beta (v - S^T k); S += k u^T; o = S^T q
 //   decay_bonus_scan   o = (S + diag(u) k v^T)^T r; S = diag(w) S + k v^T   (per-channel decay, bonus for the current token)
+//   retention_scan     S = decay_h S + k v^T; o = S^T q, q and k rotated by position
 //   head_norm_gate     per head: o / rms(o) * weight * act(gate)
 //   branch_combine     x += mean over branches of rms_unit(branch) * weight
 //
@@ -237,6 +238,9 @@ struct ScanArgs {
   float* out;
   int H, G, dk, dv, KS, tc;
   int vec;                                             // q, k (and the decay) can be read 16 bytes at a time
+  // retention: the rows' positions, the rotary frequencies [rot / 2], how many leading elements of a head are rotated,
+  // the decay of each head, and what the rotated keys are multiplied by
+  const int* pos; const float* inv_freq; int rot; const float* decay_h; float kscale;
 };
 
 template <int VE> __device__ __forceinline__ void load_vec(const float* p, float* out) {
@@ -267,7 +271,7 @@ __device__ __forceinline__ void scan_stage(const ScanArgs& a, float* buf, int DK
   const int g = MODE == 2 ? h : h / (a.H / a.G);
   const TA* x0p = (const TA*)a.q + (size_t)g * dk;                                         // q, or r
   const TA* x1p = MODE == 2 ? (const TA*)a.k + (size_t)h * dk : x0p + a.k_off;             // k
-  const float* x2p = MODE == 0 ? nullptr : a.gch + (size_t)h * dk;                          // the decay per channel
+  const float* x2p = (MODE == 0 || MODE == 3) ? nullptr : a.gch + (size_t)h * dk;           // the decay per channel
   // The values of this block's columns and the tokens' logits are asked for first and stored last: their latency
   // runs under the vectors' loads.
   constexpr int VMAX = (SC_MAX_TOK * 32 * SC_CONSUMERS + PT - 1) / PT;
@@ -283,7 +287,7 @@ __device__ __forceinline__ void scan_stage(const ScanArgs& a, float* buf, int DK
     }
   }
   float logit_b = 0.f, logit_a = 0.f;
-  if (MODE != 2 && ptid < n_tok) {
+  if (MODE < 2 && ptid < n_tok) {
     const size_t row = (size_t)(row0 + ptid);
     logit_b = a.small[row * a.lds + a.b_off + h];
     if (MODE == 0) logit_a = a.small[row * a.lds + a.a_off + h];
@@ -301,7 +305,7 @@ __device__ __forceinline__ void scan_stage(const ScanArgs& a, float* buf, int DK
         const size_t row = (size_t)(row0 + t);
         load_vec<VE>(x0p + row * a.ld + i, x0);
         load_vec<VE>(x1p + row * a.ld + i, x1);
-        if (MODE != 0) {
+        if (MODE == 1 || MODE == 2) {
 #pragma unroll
           for (int e = 0; e < VE; e += 4) *(float4*)(x2 + e) = *(const float4*)(x2p + row * ((size_t)a.H * dk) + i + e);
         }
@@ -327,7 +331,7 @@ __device__ __forceinline__ void scan_stage(const ScanArgs& a, float* buf, int DK
             const size_t row = (size_t)(row0 + t);
             x0[u] = to_f(x0p[row * a.ld + i]);
             x1[u] = to_f(x1p[row * a.ld + i]);
-            if (MODE != 0) x2[u] = x2p[row * ((size_t)a.H * dk) + i];
+            if (MODE == 1 || MODE == 2) x2[u] = x2p[row * ((size_t)a.H * dk) + i];
           }
         }
       }
@@ -343,7 +347,7 @@ __device__ __forceinline__ void scan_stage(const ScanArgs& a, float* buf, int DK
     const int idx = ptid + u * PT;
     if (idx < n_tok * COLS) V[idx] = vreg[u];
   }
-  if (MODE != 2 && ptid < n_tok) { beta[ptid] = logit_b; cc[ptid] = logit_a; }
+  if (MODE < 2 && ptid < n_tok) { beta[ptid] = logit_b; cc[ptid] = logit_a; }
   producers_sync();
   // a warp takes TPW tokens at once: their sums and butterflies are independent chains
   constexpr int TPW = SC_MAX_TOK / SC_PRODUCERS;
@@ -368,6 +372,35 @@ __device__ __forceinline__ void scan_stage(const ScanArgs& a, float* buf, int DK
     for (int u = 0; u < TPW; ++u) {
       const int t = pw + u * SC_PRODUCERS;
       if (t < n_tok && lane == 0) { cc[t] = c[u]; beta[t] = 1.f; }
+    }
+  } else if (MODE == 3) {
+    // retention: rotate the leading `rot` elements of q and k (element i with i + rot/2, angle = position * frequency i),
+    // k times kscale after the rotation; B = decay q, K = k, G = decay, c = k . q  (S^T q after the write is
+    // decay S^T q + v (k . q))
+    const int half = a.rot >> 1;
+    const float gam = a.decay_h[h];
+#pragma unroll
+    for (int u = 0; u < TPW; ++u) {
+      const int t = pw + u * SC_PRODUCERS;
+      if (t >= n_tok) continue;
+      float* Bt = B + t * DKP; float* Gt = Gd + t * DKP; float* Kt = KK + t * DKP;
+      const float p = (float)a.pos[row0 + t];
+      for (int i = lane; i < half; i += 32) {
+        float sn, cs;
+        sincosf(p * a.inv_freq[i], &sn, &cs);
+        const float qu = Bt[i], qv = Bt[i + half], ku = Kt[i], kv = Kt[i + half];
+        Bt[i] = qu * cs - qv * sn; Bt[i + half] = qv * cs + qu * sn;
+        Kt[i] = ku * cs - kv * sn; Kt[i + half] = kv * cs + ku * sn;
+      }
+      __syncwarp();
+      float kq = 0.f;
+      for (int i = lane; i < DKP; i += 32) {
+        const float kk = Kt[i] * a.kscale, qq = Bt[i];
+        kq = fmaf(kk, qq, kq);
+        Kt[i] = kk; Bt[i] = gam * qq; Gt[i] = gam;
+      }
+      kq = warp_sum(kq);
+      if (lane == 0) { cc[t] = kq; beta[t] = 1.f; }
     }
   } else {
     float sq[TPW], sk[TPW], kq[TPW];
@@ -466,7 +499,7 @@ __global__ void __launch_bounds__(SC_THREADS) scan_kernel(ScanArgs a) {
 #pragma unroll
         for (int r4 = 0; r4 < R4; ++r4) {
           const int at = t * dq + ks + KS * r4;
-          if (MODE != 2) nA[r4] = A4[at];
+          if (MODE < 2) nA[r4] = A4[at];
           nB[r4] = B4[at]; nG[r4] = G4[at]; nK[r4] = K4[at];
         }
         nv = V[t * COLS + cw]; nbeta = beta[t]; ncc = cc[t];
@@ -477,7 +510,7 @@ __global__ void __launch_bounds__(SC_THREADS) scan_kernel(ScanArgs a) {
         if (!AHEAD) fetch(t);
         float4 cA[R4], cB[R4], cG[R4], cK[R4];
 #pragma unroll
-        for (int r4 = 0; r4 < R4; ++r4) { if (MODE != 2) cA[r4] = nA[r4]; cB[r4] = nB[r4]; cG[r4] = nG[r4]; cK[r4] = nK[r4]; }
+        for (int r4 = 0; r4 < R4; ++r4) { if (MODE < 2) cA[r4] = nA[r4]; cB[r4] = nB[r4]; cG[r4] = nG[r4]; cK[r4] = nK[r4]; }
         const float v = nv, bt = nbeta, ct = ncc;
         if (AHEAD && t + 1 < n_tok) fetch(t + 1);
         float p1[4] = {0.f, 0.f, 0.f, 0.f}, p2[4] = {0.f, 0.f, 0.f, 0.f};      // four short chains a dot, added in a fixed order
@@ -485,7 +518,7 @@ __global__ void __launch_bounds__(SC_THREADS) scan_kernel(ScanArgs a) {
         for (int r4 = 0; r4 < R4; ++r4) {
           p2[0] = fmaf(S[4 * r4], cB[r4].x, p2[0]); p2[1] = fmaf(S[4 * r4 + 1], cB[r4].y, p2[1]);
           p2[2] = fmaf(S[4 * r4 + 2], cB[r4].z, p2[2]); p2[3] = fmaf(S[4 * r4 + 3], cB[r4].w, p2[3]);
-          if (MODE != 2) {
+          if (MODE < 2) {
             p1[0] = fmaf(S[4 * r4], cA[r4].x, p1[0]); p1[1] = fmaf(S[4 * r4 + 1], cA[r4].y, p1[1]);
             p1[2] = fmaf(S[4 * r4 + 2], cA[r4].z, p1[2]); p1[3] = fmaf(S[4 * r4 + 3], cA[r4].w, p1[3]);
           }
@@ -493,9 +526,9 @@ __global__ void __launch_bounds__(SC_THREADS) scan_kernel(ScanArgs a) {
         float d1 = (p1[0] + p1[1]) + (p1[2] + p1[3]), d2 = (p2[0] + p2[1]) + (p2[2] + p2[3]);
         for (int o = 1; o < KS; o <<= 1) {
           d2 += __shfl_xor_sync(0xffffffffu, d2, o);
-          if (MODE != 2) d1 += __shfl_xor_sync(0xffffffffu, d1, o);
+          if (MODE < 2) d1 += __shfl_xor_sync(0xffffffffu, d1, o);
         }
-        const float u = MODE == 2 ? v : bt * (v - d1);
+        const float u = MODE >= 2 ? v : bt * (v - d1);
         const float o = fmaf(u, ct, d2);
 #pragma unroll
         for (int r4 = 0; r4 < R4; ++r4) {
@@ -540,7 +573,7 @@ static int scan_launch(ScanArgs& a, int n_items, int max_item_rows, cudaStream_t
     bool ok = a.dk % ve == 0 && a.ld % ve == 0 && (4 * KS * R4) % ve == 0 && ((uintptr_t)a.q % 16) == 0;
     if (MODE == 2) ok = ok && ((uintptr_t)a.k % 16) == 0;
     else ok = ok && a.k_off % ve == 0;
-    if (MODE != 0) ok = ok && ((uintptr_t)a.gch % 16) == 0;
+    if (MODE == 1 || MODE == 2) ok = ok && ((uintptr_t)a.gch % 16) == 0;
     (void)esz;
     a.vec = ok ? 1 : 0;
   }
@@ -598,6 +631,23 @@ FELLM_API int fellm_decay_bonus_scan(const void* r, const void* k, const void* v
   return is_bf16 ? scan_launch<2, bf16>(a, n_items, max_item_rows, stream) : scan_launch<2, float>(a, n_items, max_item_rows, stream);
 }
 
+// Retention: S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t, q and k rotated by position (the first `rot` elements
+// of a head, element i paired with i + rot/2), k times kscale after the rotation.  qkv [T, ld]: q heads at column 0
+// (H x dk), k at k_off (H x dk), v at v_off (H x dv), as their products left them.
+FELLM_API int fellm_retention_scan(const void* qkv, int is_bf16, int ld, int k_off, int v_off, const int* positions,
+                                   const float* inv_freq, int rot, const float* decay, float kscale, float* state,
+                                   long long slot_stride, const int* item_start, const int* item_slot, float* out,
+                                   int n_items, int H, int dk, int dv, int max_item_rows, cudaStream_t stream) {
+  if (n_items <= 0) return 0;
+  if (dk < 1 || dk > 1024 || dv < 1 || H < 1 || rot < 0 || rot > dk || (rot & 1)) return FELLM_ERR_SIZE;
+  if (!qkv || !positions || !decay || !state || !item_start || !item_slot || !out || (rot && !inv_freq)) return FELLM_ERR_ARG;
+  ScanArgs a = {};
+  a.q = qkv; a.ld = ld; a.k_off = k_off; a.v_off = v_off; a.state = state; a.slot_stride = slot_stride;
+  a.item_start = item_start; a.item_slot = item_slot; a.out = out; a.H = H; a.G = H; a.dk = dk; a.dv = dv;
+  a.pos = positions; a.inv_freq = inv_freq; a.rot = rot; a.decay_h = decay; a.kscale = kscale;
+  return is_bf16 ? scan_launch<3, bf16>(a, n_items, max_item_rows, stream) : scan_launch<3, float>(a, n_items, max_item_rows, stream);
+}
+
 // ---------------------------------------------------------------- per-head norm and gate
 // y[t, h, e] = o[t, h, e] / sqrt(mean_e o^2 + eps) * w[(per_head ? h * dv : 0) + e] * act(gate[t, h*dv + e]);
 // act: 0 no gate, 1 SiLU, 2 sigmoid.  One warp per (t, h).
@@ -614,10 +664,11 @@ head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, 
   for (int e = lane; e < dv; e += 32) { float v = orow[e]; ss = fmaf(v, v, ss); }
   ss = warp_sum(ss);
   const float scale = 1.0f / sqrtf(ss / (float)dv + eps);
-  const float* wr = w + (per_head ? (size_t)h * dv : 0);
+  const float* wr = w ? w + (per_head ? (size_t)h * dv : 0) : nullptr;       // no weight: the unit norm alone
   TO* yr = y + ((size_t)t * H + h) * dv;
   for (int e = lane; e < dv; e += 32) {
-    float v = (orow[e] * scale) * wr[e];
+    float v = orow[e] * scale;
+    if (wr) v *= wr[e];
     if (act) {
       float gz = to_f(gate[(size_t)t * ldg + (size_t)h * dv + e]);
       v *= act == 1 ? silu_f(gz) : sigmoid_f(gz);
@@ -629,7 +680,7 @@ head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, 
 FELLM_API int fellm_head_norm_gate(const float* o, const float* w, int per_head, const void* gate, int gate_bf16, int ldg,
                                    int act, void* y, int y_bf16, int T, int H, int dv, float eps, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (!o || !w || !y || (act && !gate)) return FELLM_ERR_ARG;
+  if (!o || !y || (act && !gate)) return FELLM_ERR_ARG;
   unsigned blocks = (unsigned)(((long long)T * H + 3) / 4);
 #define HNG(TO_, TG_) head_norm_gate_kernel<TO_, TG_><<<blocks, 128, 0, stream>>>(o, w, per_head, (const TG_*)gate, ldg, act, (TO_*)y, T, H, dv, eps)
   if (y_bf16) { if (gate_bf16) HNG(bf16, bf16); else HNG(bf16, float); }

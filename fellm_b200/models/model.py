@@ -63,6 +63,16 @@ def _prenorm(block, x, ctx, cache, act_dtype, reads_only):
         block.ffn.forward(h, ctx, x)
 
 
+@register_arrangement("parallel")
+def _parallel(block, x, ctx, cache, act_dtype, reads_only):
+    """h = norm1(x); x += mixer(h) + ffn(h): one norm, both sublayers read its output (each adds into x, the mixer
+    first)."""
+    h = block.norm1.forward(x, act_dtype)
+    block.mixer.forward(h, ctx, cache, x, reads_only=reads_only)
+    if block.ffn is not None:
+        block.ffn.forward(h, ctx, x)
+
+
 def _with_children(part):
     return [part] + [q for c in part.children() for q in _with_children(c)]
 
@@ -174,7 +184,7 @@ class Model:
         ops.forget_norm_handoff()
         x = self.embedding.forward(ctx.tokens, ctx.status)
         # a connector reads the embedding's output again later; the blocks update x in place
-        x0 = x.clone() if self.connectors else None
+        x0 = x.clone() if any(c.needs_embedding for c in self.connectors) else None
         for n, run in enumerate(self.schedule):
             src = n if run.cache_of is None else run.cache_of
             if run.before is not None:

@@ -91,18 +91,39 @@ def _i32(t, name):
 
 # ------------------------------------------------------------------------------ elementwise
 
-def embed_rows(tokens, table, out, status=None):
-    """out[t, :] = float32(table[tokens[t], :]).  A token outside the table writes zeros and sets
+def embed_rows(tokens, table, out, status=None, scale: float = 1.0):
+    """out[t, :] = float32(table[tokens[t], :]) * scale.  A token outside the table writes zeros and sets
     status to 1 (the host checks ids first; the kernel never reads out of bounds)."""
     _dev(tokens, table, out)
     _i32(tokens, "tokens")
     T, d = out.shape
     assert out.dtype == torch.float32 and out.is_contiguous() and table.is_contiguous()
     assert table.shape[1] == d and tokens.numel() == T
-    f = _fn("elementwise", "fellm_embed_rows", [_c_p, _c_p, _c_int, _c_p, _c_int, _c_int, _c_int, _c_p, _c_p])
-    _check(f(_p(tokens), _p(table), _is_bf16(table), _p(out), T, d, table.shape[0], _p(status), _stream()),
+    f = _fn("elementwise", "fellm_embed_rows", [_c_p, _c_p, _c_int, _c_p, _c_int, _c_int, _c_int, _c_p, _c_f, _c_p])
+    _check(f(_p(tokens), _p(table), _is_bf16(table), _p(out), T, d, table.shape[0], _p(status), float(scale), _stream()),
            "embed_rows")
     return out
+
+
+def add_row_vector(x, v):
+    """x float32 [T, d] += v float32 [d], every row."""
+    _dev(x, v)
+    assert x.dtype == torch.float32 and v.dtype == torch.float32 and x.is_contiguous() and v.is_contiguous()
+    T, d = x.shape
+    assert v.numel() == d
+    residual_written(x)
+    f = _fn("elementwise", "fellm_add_row_vector", [_c_p, _c_p, _c_int, _c_int, _c_p])
+    _check(f(_p(x), _p(v), T, d, _stream()), "add_row_vector")
+    return x
+
+
+def scale_softcap(z, scale: float = 1.0, cap=None):
+    """z float32, in place: z * scale, then cap * tanh(. / cap) where a cap is given."""
+    _dev(z)
+    assert z.dtype == torch.float32 and z.is_contiguous()
+    f = _fn("elementwise", "fellm_scale_softcap", [_c_p, ctypes.c_longlong, _c_f, _c_f, _c_p])
+    _check(f(_p(z), z.numel(), float(scale), float(cap or 0.0), _stream()), "scale_softcap")
+    return z
 
 
 def rmsnorm(x, w, eps: float, out_dtype, rows=None, out=None):
@@ -431,6 +452,33 @@ def decay_bonus_scan(r, k, v, w, u, state, item_start, item_slot, n_items, H, dk
     return out
 
 
+def retention_scan(qkv, k_off, v_off, positions, inv_freq, rot_dim, decay, kscale, state, item_start, item_slot, n_items,
+                   H, dk, dv, out=None, max_item_rows=0):
+    """Retention over portions: per head S = decay[h] S + k v^T, o = S^T q, with q and k rotated by position (the first
+    rot_dim elements of a head, element i paired with i + rot_dim/2, inv_freq float32 [rot_dim/2]) and k times kscale
+    after the rotation.  qkv [T, >= v_off + H*dv]: q at column 0 (H x dk), k at k_off, v at v_off (H x dv).
+    state float32 [slots, ..., H, dk, dv] (a slot's states lie slot_stride apart).  Returns float32 [T, H*dv]."""
+    _dev(qkv, positions, inv_freq, decay, state, item_start, item_slot)
+    T = qkv.shape[0]
+    assert qkv.stride(1) == 1 and decay.dtype == torch.float32 and decay.numel() == H and decay.is_contiguous()
+    assert rot_dim % 2 == 0 and 0 <= rot_dim <= dk
+    if rot_dim:
+        assert inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dim // 2 and inv_freq.is_contiguous()
+    _i32(positions, "positions"), _i32(item_start, "item_start"), _i32(item_slot, "item_slot")
+    if dk > MAX_SCAN_KEY_DIM:
+        raise KernelError(f"retention_scan: key size {dk} is above {MAX_SCAN_KEY_DIM}")
+    if out is None:
+        out = torch.empty((T, H * dv), dtype=torch.float32, device=qkv.device)
+    st, stride = _state_args(state)
+    f = _fn("recurrent", "fellm_retention_scan",
+            [_c_p, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p, _c_int, _c_p, _c_f, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int,
+             _c_int, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_p(qkv), _is_bf16(qkv), qkv.stride(0), k_off, v_off, _p(positions), _p(inv_freq) if rot_dim else None,
+             rot_dim, _p(decay), float(kscale), st, stride, _p(item_start), _p(item_slot), _p(out), n_items, H, dk, dv,
+             int(max_item_rows), _stream()), "retention_scan")
+    return out
+
+
 _GATE_ACT = {None: 0, "silu": 1, "sigmoid": 2}
 
 
@@ -439,8 +487,9 @@ def head_norm_gate(o, w, per_head: bool, gate, gate_act, eps: float, H: int, dv:
     [H*dv] (per_head); gate [T, H*dv] (row stride free), any engine dtype; gate_act 'silu' | 'sigmoid' | None."""
     _dev(o, w, gate)
     T = o.shape[0]
-    assert o.dtype == torch.float32 and o.is_contiguous() and w.dtype == torch.float32
-    assert w.numel() == (H * dv if per_head else dv)
+    assert o.dtype == torch.float32 and o.is_contiguous()
+    if w is not None:                    # None: the unit norm alone
+        assert w.dtype == torch.float32 and w.numel() == (H * dv if per_head else dv)
     if gate_act is not None:
         assert gate is not None and gate.stride(1) == 1 and gate.shape == (T, H * dv)
     if out is None:
@@ -465,6 +514,88 @@ def branch_combine(x, branches, weights, eps: float):
     f = _fn("recurrent", "fellm_branch_combine", [_c_p, _c_p, _c_int, _c_p, _c_int, _c_int, _c_f, _c_p])
     _check(f(arr(*[o.data_ptr() for o in branches]), arr(*[w.data_ptr() for w in weights]), n, _p(x), T, d, float(eps),
              _stream()), "branch_combine")
+    return x
+
+
+
+# ------------------------------------------------------------------------------ routed experts
+
+MOE_ROW_TILE = 64            # rows of a tile of the grouped products (both kernels)
+MOE_PLAN_TILE = 1024
+MOE_MAX_TOP = 16
+MOE_MMA = os.environ.get("FELLM_B200_MOE_MMA", "1") != "0"
+
+
+def moe_route(logits, E: int, top: int, renormalize: bool = False):
+    """logits float32 [T, >= E] -> (idx int32 [T, top], w float32 [T, top]): the `top` experts with the largest
+    softmax scores over all E (ties: the lower expert) and those scores as they are, or renormalised to sum 1."""
+    _dev(logits)
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    if not 1 <= top <= min(E, MOE_MAX_TOP):
+        raise KernelError(f"moe_route: top {top} must be in 1..{min(E, MOE_MAX_TOP)}")
+    T = logits.shape[0]
+    idx = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    w = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    f = _fn("moe", "fellm_moe_route", [_c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p])
+    _check(f(_p(logits), logits.stride(0), T, E, top, int(renormalize), _p(idx), _p(w), _stream()), "moe_route")
+    return idx, w
+
+
+class MoePlan:
+    """The (token, choice) pairs of a step sorted by expert: sorted[place] = pair, place_of[pair] = place, and the
+    table of row tiles (expert, first row, rows) with their count on the device; max_tiles bounds it on the host."""
+    __slots__ = ("sorted", "place_of", "table", "n_tiles", "max_tiles", "pairs", "top")
+
+
+def moe_plan(idx, E: int) -> MoePlan:
+    _dev(idx)
+    _i32(idx, "idx")
+    assert idx.is_contiguous()
+    T, top = idx.shape
+    P = T * top
+    tiles = -(-P // MOE_PLAN_TILE)
+    plan = MoePlan()
+    plan.pairs, plan.top = P, top
+    plan.max_tiles = min(P, E) + P // MOE_ROW_TILE
+    ints = torch.empty(2 * tiles * E + P + 2 * P + 3 * plan.max_tiles + 1, dtype=torch.int32, device=idx.device)
+    at = 2 * tiles * E + P
+    scratch = ints[:at]
+    plan.sorted, plan.place_of = ints[at:at + P], ints[at + P:at + 2 * P]
+    plan.table = ints[at + 2 * P:at + 2 * P + 3 * plan.max_tiles]
+    plan.n_tiles = ints[at + 2 * P + 3 * plan.max_tiles:]
+    f = _fn("moe", "fellm_moe_plan", [_c_p, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p])
+    _check(f(_p(idx), P, E, MOE_ROW_TILE, _p(scratch), _p(plan.sorted), _p(plan.place_of), _p(plan.table),
+             _p(plan.n_tiles), _stream()), "moe_plan")
+    return plan
+
+
+def moe_gemm(a, w, plan: MoePlan, *, gated: bool, gather: bool, out_dtype=None):
+    """Grouped product over a plan's row tiles.  w [E, (2 if gated else 1) * N, K]; gather: row r of the result
+    reads a[token of the pair sorted r] (a [T, K]); else a [P, K] is in sorted order.  gated: SiLU(gate) * up in
+    a's dtype; else float32.  Returns [P, N] in sorted order."""
+    _dev(a, w)
+    assert a.stride(1) == 1 and w.is_contiguous() and a.dtype == w.dtype
+    E, n_rows, K = w.shape
+    N = n_rows // 2 if gated else n_rows
+    assert a.shape[1] == K
+    out = torch.empty((plan.pairs, N), dtype=a.dtype if gated else torch.float32, device=a.device)
+    f = _fn("moe", "fellm_moe_gemm", [_c_p, _c_int, _c_int, _c_p, _c_int, _c_p, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int,
+                                      _c_int, _c_p, _c_p, _c_int, _c_int, _c_p])
+    _check(f(_p(a), _is_bf16(a), a.stride(0), _p(plan.sorted) if gather else None, plan.top, _p(w), _is_bf16(w), _p(out),
+             _is_bf16(out), N, N, K, int(gated), _p(plan.table), _p(plan.n_tiles), plan.max_tiles, int(MOE_MMA), _stream()),
+           "moe_gemm")
+    return out
+
+
+def moe_combine(x, y, plan: MoePlan, w):
+    """x float32 [T, d] += sum over a token's choices c, in order, of w[t, c] * y[place of (t, c)]."""
+    _dev(x, y, w)
+    T, d = x.shape
+    assert x.dtype == torch.float32 and y.dtype == torch.float32 and w.dtype == torch.float32
+    assert x.is_contiguous() and y.is_contiguous() and w.is_contiguous() and y.shape == (plan.pairs, d)
+    residual_written(x)
+    f = _fn("moe", "fellm_moe_combine", [_c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_p(x), _p(y), _p(plan.place_of), _p(w), T, plan.top, d, _stream()), "moe_combine")
     return x
 
 
@@ -549,13 +680,18 @@ def kv_write(src, k_off, v_off, pool, block_table, positions, row_slot, layer, p
 
 
 def paged_attention_general(q, H, hd, vd, pool, block_table, positions, row_slot, layer, page_tokens, G, scale, *,
-                            window=None, chunk=None, softcap=None, gate=None, out=None):
+                            window=None, chunk=None, softcap=None, gate=None, slopes=None, q_temp=None, out=None):
     """Attention on CUDA cores with float32 arithmetic for every form the part describes: q read in place from rows
     [T, >= H*hd] (heads at column 0), values of size vd, scores soft-capped (softcap * tanh(s / softcap)), keys limited
     to the last `window` positions and to the query's own block of `chunk` positions, and gate float32 [T, >= H]
-    whose sigmoid scales each head's output.  Returns [T, H*vd] in q's dtype."""
-    _dev(q, pool, block_table, positions, row_slot, gate)
+    whose sigmoid scales each head's output.  slopes float32 [H]: slopes[h] * (query position - key position) is
+    taken off the scaled score.  q_temp = (coef, every): the query at position p is multiplied by
+    1 + coef ln(floor((p + 1) / every) + 1).  vd == 0: the values are the keys (a page-layer record holds keys alone).
+    Returns [T, H*vd] (H*hd when the values are the keys) in q's dtype."""
+    _dev(q, pool, block_table, positions, row_slot, gate, slopes)
     T = q.shape[0]
+    if slopes is not None:
+        assert slopes.dtype == torch.float32 and slopes.numel() == H and slopes.is_contiguous()
     if hd > 256 or vd > 256:
         raise KernelError(f"attention: head sizes {hd} / {vd} are above the kernel's maximum 256")
     if H % G:
@@ -565,14 +701,16 @@ def paged_attention_general(q, H, hd, vd, pool, block_table, positions, row_slot
     if gate is not None:
         assert gate.dtype == torch.float32 and gate.stride(1) == 1
     if out is None:
-        out = torch.empty((T, H * vd), dtype=q.dtype, device=q.device)
+        out = torch.empty((T, H * (vd or hd)), dtype=q.dtype, device=q.device)
+    qt_coef, qt_every = q_temp if q_temp else (0.0, 0)
     f = _fn("attention_simt", "fellm_paged_attention_general",
             [_c_p, _c_int, _c_p, _c_int, _c_p, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
-             _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_f, _c_int, _c_p, _c_int, _c_p])
+             _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_f, _c_int, _c_p, _c_int, _c_p, _c_f, _c_int, _c_p])
     _check(f(_p(q), _is_bf16(q), _p(pool), _is_bf16(pool), _p(block_table), block_table.shape[1],
              _p(positions), _p(row_slot), _p(out), T, H, G, hd, page_tokens, layer, pool.shape[1],
              float(scale), int(window or 0), vd, q.stride(0), float(softcap or 0.0), int(chunk or 0), _p(gate),
-             gate.stride(0) if gate is not None else 0, _stream()), "paged_attention_general")
+             gate.stride(0) if gate is not None else 0, _p(slopes), float(qt_coef), int(qt_every), _stream()),
+           "paged_attention_general")
     return out
 
 

@@ -6,9 +6,12 @@ cache; scores scaled by 1/sqrt(hd); kv head g = h // (H/G); causal, optionally w
 Beyond FeLLM's attention the part takes, as parameters: a scale of its own, a soft cap on the scores
 (cap * tanh(s / cap)), values of another size than keys (v_dim), blocks of `chunk` positions that a
 query does not look out of (counted from position 0 of the sequence), and a gate per head,
-sigmoid(W_g h), on the head's output before W_o.  Any of these sends the layer to the general
-attention kernel (CUDA cores, float32 arithmetic, both engine dtypes); without them the tensor-core
-kernels run as before."""
+sigmoid(W_g h), on the head's output before W_o; biases on the q, k (v) and output projections; values
+that are the keys themselves (no W_v, and the cache keeps the keys alone); a bias by distance taken
+off the scaled score, slope_h (i - j) with slope_h = 2^(-slope_exp (h + 1) / H); and a query
+temperature by position, q times 1 + coef ln(floor((p + 1) / every) + 1).  Any of these but the
+biases sends the layer to the general attention kernels (float32 softmax in both engine dtypes);
+without them the tensor-core kernels run as before."""
 from __future__ import annotations
 
 import math
@@ -25,7 +28,8 @@ from .linear import linear, linear_modules
 class Attention(Mixer):
     def __init__(self, *, dtype: str, size: int, heads: int, kv_heads: int, head_dim: int, qk_norm: bool,
                  norm_eps: float, position, window=None, shares_cache: bool = False, scale=None, softcap=None,
-                 v_dim=None, chunk=None, head_gate: bool = False):
+                 v_dim=None, chunk=None, head_gate: bool = False, bias: bool = False, values_are_keys: bool = False,
+                 slope_exp=None, q_temp=None):
         """`position`: a PartSpec of the 'position' category.  `shares_cache`: this layer keeps no
         keys and values (it has no k/v weights) and reads those of the run its schedule entry
         names."""
@@ -33,7 +37,8 @@ class Attention(Mixer):
         self.size, self.H, self.G, self.hd = int(size), int(heads), int(kv_heads), int(head_dim)
         if self.H % self.G:
             raise ConfigError(f"attention: {self.H} heads are not a multiple of {self.G} kv heads")
-        general = bool(softcap or chunk or head_gate or (v_dim is not None and int(v_dim) != self.hd))
+        general = bool(softcap or chunk or head_gate or (v_dim is not None and int(v_dim) != self.hd) or bias
+                       or values_are_keys or slope_exp or q_temp)
         if general and not 1 <= self.hd <= 256:
             raise ConfigError(f"attention: head_dim {self.hd} must be in 1..256")
         if not general and (self.hd % 16 or not 16 <= self.hd <= 256):       # the tensor-core kernels' sizes
@@ -55,7 +60,17 @@ class Attention(Mixer):
         self.vd = self.hd if v_dim is None else int(v_dim)
         self.chunk = None if chunk is None else int(chunk)
         self.head_gate = bool(head_gate)
-        self.general = bool(self.softcap or self.vd != self.hd or self.chunk or self.head_gate)
+        self.bias, self.values_are_keys = bool(bias), bool(values_are_keys)
+        self.slope_exp = None if not slope_exp else float(slope_exp)
+        self.q_temp = None
+        if q_temp:
+            coef, every = q_temp
+            if int(every) < 1:
+                raise ConfigError(f"attention: the query temperature's step {every} must be positive")
+            self.q_temp = (float(coef), int(every))
+        if self.values_are_keys and self.vd != self.hd:
+            raise ConfigError(f"attention: values that are the keys have the keys' size {self.hd}, not {self.vd}")
+        self.general = general
         if self.general:
             if self.qk_norm or self.position.inv_freq is not None or self.shares_cache:
                 raise ConfigError("attention: a soft cap, v_dim, chunk or head gate goes with no QK norm, no rotation "
@@ -65,7 +80,14 @@ class Attention(Mixer):
         d, H, G, hd = self.size, self.H, self.G, self.hd
         self.decls = {"q_proj.weight": ParamDecl((H * hd, d)), "out_proj.weight": ParamDecl((d, H * self.vd))}
         if not self.shares_cache:
-            self.decls.update({"k_proj.weight": ParamDecl((G * hd, d)), "v_proj.weight": ParamDecl((G * self.vd, d))})
+            self.decls["k_proj.weight"] = ParamDecl((G * hd, d))
+            if not self.values_are_keys:
+                self.decls["v_proj.weight"] = ParamDecl((G * self.vd, d))
+        if self.bias:
+            rows = {"q_proj": H * hd, "k_proj": G * hd, "v_proj": G * self.vd, "out_proj": d}
+            for name, n in rows.items():
+                if name + ".weight" in self.decls:
+                    self.decls[name + ".bias"] = ParamDecl((n,), role="vector", init=("normal", 0.01))
         if self.head_gate:
             self.decls["gate.weight"] = ParamDecl((H, d), init=("normal", 0.1))
         if self.qk_norm:
@@ -76,20 +98,32 @@ class Attention(Mixer):
     takes_lazy_norm = True
 
     def cache_need(self):
-        return PagedKV(self.G, self.hd, self.window, self.chunk, None if self.vd == self.hd else self.vd)
+        return PagedKV(self.G, self.hd, self.window, self.chunk, None if self.vd == self.hd else self.vd,
+                       self.values_are_keys)
 
     def prepare(self):
         q = self.w.pop("q_proj.weight")
         if self.shares_cache:
             self.w["qkv.weight"] = q.contiguous()
         else:
-            k, v = self.w.pop("k_proj.weight"), self.w.pop("v_proj.weight")
-            if not (q.dtype == k.dtype == v.dtype):
-                q, k, v = q.float(), k.float(), v.float()
-            self.w["qkv.weight"] = torch.cat([q, k, v], dim=0).contiguous()      # [(H+2G)*hd, d]
+            mats = [q, self.w.pop("k_proj.weight")] + ([] if self.values_are_keys else [self.w.pop("v_proj.weight")])
+            if any(m.dtype != q.dtype for m in mats):
+                mats = [m.float() for m in mats]
+            self.w["qkv.weight"] = torch.cat(mats, dim=0).contiguous()      # [(H+2G)*hd, d]; [(H+G)*hd, d] without W_v
+        if self.bias:
+            names = ["q_proj.bias"] + ([] if self.shares_cache else ["k_proj.bias"] + ([] if self.values_are_keys else ["v_proj.bias"]))
+            self.w["qkv.bias"] = torch.cat([self.w.pop(n) for n in names]).contiguous()
         if self.general:
             from .gated_delta import _pad_rows
+            n = self.w["qkv.weight"].shape[0]
             self.w["qkv.weight"] = _pad_rows(self.w["qkv.weight"])
+            if self.bias:
+                extra = self.w["qkv.weight"].shape[0] - n
+                self.w["qkv.bias"] = torch.cat([self.w["qkv.bias"], self.w["qkv.bias"].new_zeros(extra)]).contiguous()
+            if self.slope_exp is not None:
+                # float64 on the host, rounded once
+                self.w["slopes"] = torch.tensor([2.0 ** (-self.slope_exp * (h + 1) / self.H) for h in range(self.H)],
+                                                dtype=torch.float64).to(torch.float32).to(q.device)
             if self.head_gate:
                 self.w["gate.weight"] = _pad_rows(self.w["gate.weight"])
         self.position.to(q.device)
@@ -128,10 +162,13 @@ class Attention(Mixer):
         part's scale, cap, window, chunk and gate."""
         H, G, hd, vd = self.H, self.G, self.hd, self.vd
         gate = linear(xn, self.w["gate.weight"], out_dtype=torch.float32) if self.head_gate else None
-        qkv = linear(xn, self.w["qkv.weight"])
+        qkv = linear(xn, self.w["qkv.weight"], self.w.get("qkv.bias"))
+        if self.values_are_keys:
+            vd = 0              # nothing is kept beside the keys; the read-out has their size
         ops.kv_write(qkv, H * hd, (H + G) * hd, cache.pool, cache.block_table, ctx.positions, ctx.row_slot, cache.layer,
                      cache.page_tokens, G, hd, vd, status=ctx.status)
-        if self._on_tensor_cores(qkv) and not ctx.all_single:
+        plain = not (self.values_are_keys or self.slope_exp is not None or self.q_temp)
+        if plain and self._on_tensor_cores(qkv) and not ctx.all_single:
             # portions of prompts: the tensor-core kernel (keys and values of one size)
             a = ops.attention_prefill_general(qkv, H, cache.pool, cache.block_table, ctx.positions, ctx.row_slot,
                                               ctx.item_start, ctx.n_items, ctx.max_item_rows, cache.layer, self.scale,
@@ -139,8 +176,9 @@ class Attention(Mixer):
         else:
             a = ops.paged_attention_general(qkv, H, hd, vd, cache.pool, cache.block_table, ctx.positions, ctx.row_slot,
                                             cache.layer, cache.page_tokens, G, self.scale, window=self.window,
-                                            chunk=self.chunk, softcap=self.softcap, gate=gate)
-        linear(a, self.w["out_proj.weight"], out=out, accumulate=True)
+                                            chunk=self.chunk, softcap=self.softcap, gate=gate,
+                                            slopes=self.w.get("slopes"), q_temp=self.q_temp)
+        linear(a, self.w["out_proj.weight"], self.w.get("out_proj.bias"), out=out, accumulate=True)
         return out
 
     def _on_tensor_cores(self, qkv) -> bool:

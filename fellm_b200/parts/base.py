@@ -61,15 +61,20 @@ class PagedKV:
     latest positions a query reads (None: all of them).  `chunk`: a query reads only keys of its
     own block of `chunk` positions, counted from position 0 (None: no such blocks).  `v_dim`: the
     size of a value where it differs from a key's (None: head_dim); a page-layer record is then the
-    keys [kv_heads][page_tokens][head_dim] followed by the values [kv_heads][page_tokens][v_dim]."""
+    keys [kv_heads][page_tokens][head_dim] followed by the values [kv_heads][page_tokens][v_dim].
+    `values_are_keys`: the layer reads its keys as its values too; a record holds the keys alone."""
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
     chunk: Optional[int] = None
     v_dim: Optional[int] = None
+    values_are_keys: bool = False
 
     @property
     def value_dim(self) -> int:
+        """What a record keeps of a value per head and token (0: nothing beside the key)."""
+        if self.values_are_keys:
+            return 0
         return self.head_dim if self.v_dim is None else self.v_dim
 
 
@@ -163,7 +168,9 @@ class FeedForward(Part):
 class Connector(Part):
     """Rewrites the residual stream between two blocks (e.g. where a looped run of layers starts a
     pass): forward(x, x0, step) returns the new float32 [T, d] stream; x0 is the embedding's output,
-    `step` the number of the pass."""
+    `step` the number of the pass.  needs_embedding = False: the connector never reads x0 (the model then keeps no
+    copy of the embedding's output)."""
+    needs_embedding = True
 
     def forward(self, x: torch.Tensor, x0: torch.Tensor, step: int, act_dtype: torch.dtype) -> torch.Tensor:
         raise NotImplementedError

@@ -2,7 +2,9 @@
 
 'concat_proj': x <- W [x ; x0] + step[t], with x0 the embedding's output and t the number of the
 pass that starts: the entry of a pass of a looped run of layers (the same weights run several
-times in a row, each pass with caches of its own)."""
+times in a row, each pass with caches of its own).
+
+'add_step': x <- x + step[t]: the same entry without a projection and without the embedding."""
 from __future__ import annotations
 
 import torch
@@ -30,3 +32,19 @@ class ConcatProjection(Connector):
 
     def kernel_modules(self, dtype):
         return linear_modules(dtype) + [("elementwise", None)]
+
+
+@register_part("connector", "add_step")
+class AddStep(Connector):
+    needs_embedding = False
+
+    def __init__(self, *, dtype: str, size: int, steps: int):
+        super().__init__()
+        self.size, self.steps = int(size), int(steps)
+        self.decls = {"step": ParamDecl((self.steps, self.size), role="vector", init=("normal", 0.05))}
+
+    def forward(self, x, x0, step, act_dtype):
+        return ops.add_row_vector(x, self.w["step"][step])
+
+    def kernel_modules(self, dtype):
+        return [("elementwise", None)]

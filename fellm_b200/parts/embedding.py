@@ -1,6 +1,7 @@
-"""Token embedding (no scaling, promoted to float32: crates/fellm-model/src/graph.rs:58-65) and
-the output head (final norm is a Norm part; logits = W xf in float32, W = the embedding matrix
-when tied: graph.rs:29-39,111-131)."""
+"""Token embedding (promoted to float32: crates/fellm-model/src/graph.rs:58-65; times `scale`, 1 for FeLLM's
+models) and the output head (final norm is a Norm part; logits = W xf in float32, W = the embedding matrix
+when tied: graph.rs:29-39,111-131; then times `logit_scale` and soft-capped, cap tanh(z / cap), where a
+design asks for it)."""
 from __future__ import annotations
 
 import torch
@@ -12,14 +13,14 @@ from .linear import LazyNorm, linear, linear_modules
 
 @register_part("embedding", "table")
 class TableEmbedding(Embedding):
-    def __init__(self, *, dtype: str, vocab: int, size: int):
+    def __init__(self, *, dtype: str, vocab: int, size: int, scale: float = 1.0):
         super().__init__()
-        self.vocab, self.size = int(vocab), int(size)
+        self.vocab, self.size, self.scale = int(vocab), int(size), float(scale)
         self.decls = {"weight": ParamDecl((self.vocab, self.size))}
 
     def forward(self, tokens, status=None):
         out = torch.empty((tokens.numel(), self.size), dtype=torch.float32, device=tokens.device)
-        return ops.embed_rows(tokens, self.w["weight"], out, status)
+        return ops.embed_rows(tokens, self.w["weight"], out, status, self.scale)
 
     def kernel_modules(self, dtype):
         return [("elementwise", None)]
@@ -29,15 +30,19 @@ class TableEmbedding(Embedding):
 class LinearHead(Head):
     """tied=True: owns no tensor; the model hands it the embedding matrix."""
 
-    def __init__(self, *, dtype: str, vocab: int, size: int, tied: bool):
+    def __init__(self, *, dtype: str, vocab: int, size: int, tied: bool, logit_scale: float = 1.0, softcap=None):
         super().__init__()
         self.vocab, self.size, self.tied = int(vocab), int(size), bool(tied)
+        self.logit_scale, self.softcap = float(logit_scale), (float(softcap) if softcap else None)
         self.decls = {} if self.tied else {"weight": ParamDecl((self.vocab, self.size))}
 
     takes_lazy_norm = True
 
     def forward(self, xf):
-        return linear(xf, self.w["weight"], out_dtype=torch.float32)
+        z = linear(xf, self.w["weight"], out_dtype=torch.float32)
+        if self.logit_scale != 1.0 or self.softcap is not None:
+            ops.scale_softcap(z, self.logit_scale, self.softcap)
+        return z
 
     def reserve(self, device, max_rows, n_ctx):
         # best (value, index) of every CTA's part of a row, for greedy steps that skip the logits
@@ -46,8 +51,8 @@ class LinearHead(Head):
     def forward_greedy(self, xf, out_tokens):
         w = self.w["weight"]
         keys = getattr(self, "_argmax_keys", None)
-        if keys is None or w.dtype != torch.bfloat16 or not ops.FUSED_ARGMAX:
-            return False
+        if keys is None or w.dtype != torch.bfloat16 or not ops.FUSED_ARGMAX or self.logit_scale <= 0.0:
+            return False                 # (a positive scale and the soft cap keep the order of a row's logits)
         rows = xf.shape[0]
         h = xf.handed_on() if isinstance(xf, LazyNorm) else None
         if h is not None and ops.row_scale_takes(rows, w.shape[0], w.shape[1]):
@@ -72,4 +77,4 @@ class LinearHead(Head):
         return [self.w["weight"]]
 
     def kernel_modules(self, dtype):
-        return linear_modules(dtype)
+        return linear_modules(dtype) + [("elementwise", None)]

@@ -1,0 +1,63 @@
+"""Routed experts: a feed-forward made of `experts` small gated feed-forwards of which every token uses `top`.
+
+    z = W_router h, float32;  s = softmax(z) over all experts
+    the `top` experts with the largest scores are chosen (ties: the lower expert)
+    weights = their scores as they are (renormalize=True: divided by their sum)
+    out = sum over the chosen experts, in the order of their scores, of weight * W_down (SiLU(W_gate h) * (W_up h))
+
+Experts have no biases.  Nothing goes through the host: the router's choices are sorted by expert on the device
+(ops.moe_plan) and two grouped products walk the sorted rows, the first gathering its input rows by token and
+applying SiLU(gate) * up in its epilogue, the second leaving float32 rows that ops.moe_combine adds, weighted, into
+the residual stream.  A token's result does not depend on what else is in the step.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..config.errors import ConfigError
+from .base import FeedForward, ParamDecl, register_part
+from .gated_delta import _pad_rows
+from .linear import linear, linear_modules
+
+
+@register_part("feed_forward", "moe")
+class RoutedExperts(FeedForward):
+    def __init__(self, *, dtype: str, size: int, ff: int, experts: int, top: int, renormalize: bool = False):
+        super().__init__()
+        self.size, self.ff, self.E, self.top = int(size), int(ff), int(experts), int(top)
+        self.renormalize = bool(renormalize)
+        if not 1 <= self.top <= min(self.E, ops.MOE_MAX_TOP):
+            raise ConfigError(f"moe: top {self.top} must be in 1..{min(self.E, ops.MOE_MAX_TOP)} ({self.E} experts)")
+        self.decls = {"router.weight": ParamDecl((self.E, self.size), init=("normal", 0.5))}
+        for e in range(self.E):
+            self.decls[f"e{e}.gate.weight"] = ParamDecl((self.ff, self.size))
+            self.decls[f"e{e}.up.weight"] = ParamDecl((self.ff, self.size))
+            self.decls[f"e{e}.down.weight"] = ParamDecl((self.size, self.ff))
+
+    def prepare(self):
+        w = self.w
+        mats = [w.pop(f"e{e}.{n}.weight") for e in range(self.E) for n in ("gate", "up", "down")]
+        dt = mats[0].dtype if all(m.dtype == mats[0].dtype for m in mats) else torch.float32
+        gu = [torch.cat([mats[3 * e].to(dt), mats[3 * e + 1].to(dt)], 0) for e in range(self.E)]
+        w["gate_up.weight"] = torch.stack(gu, 0).contiguous()                                  # [E, 2 ff, d]: gate rows, then up
+        w["down.weight"] = torch.stack([mats[3 * e + 2].to(dt) for e in range(self.E)], 0).contiguous()     # [E, d, ff]
+        w["router.weight"] = _pad_rows(w["router.weight"])
+
+    def forward(self, hn, ctx, out):
+        w = self.w
+        z = linear(hn, w["router.weight"], out_dtype=torch.float32)
+        idx, score = ops.moe_route(z, self.E, self.top, self.renormalize)
+        plan = ops.moe_plan(idx, self.E)
+        if hn.dtype != w["gate_up.weight"].dtype:          # a file that stores some experts in 32-bit under a bfloat16 engine
+            hn = hn.to(w["gate_up.weight"].dtype)
+        a = ops.moe_gemm(hn, w["gate_up.weight"], plan, gated=True, gather=True)
+        y = ops.moe_gemm(a, w["down.weight"], plan, gated=False, gather=False)
+        ops.moe_combine(out, y, plan, score)
+        return out
+
+    def weight_order(self):
+        return [self.w["router.weight"], self.w["gate_up.weight"], self.w["down.weight"]]
+
+    def kernel_modules(self, dtype):
+        return linear_modules(dtype) + [("moe", None)]

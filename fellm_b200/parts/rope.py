@@ -23,13 +23,19 @@ class NoPosition(PositionEncoding):
 
 @register_part("position", "rope")
 class Rotary(PositionEncoding):
-    def __init__(self, *, dtype: str, rot_dim: int, theta: float, pairing: str):
+    def __init__(self, *, dtype: str, rot_dim: int, theta: float, pairing: str, table64: bool = False):
+        """table64: the frequencies are computed in float64 and rounded once (default: float32 powers, as FeLLM's)."""
         super().__init__()
         if rot_dim % 2:
             raise ConfigError(f"rotary dimension {rot_dim} must be even")
         if pairing not in ("adjacent", "split_half"):
             raise ConfigError(f"unknown rotary pairing {pairing!r}")
         self.rot_dim, self.theta, self.pairing = int(rot_dim), float(theta), pairing
+        if table64:
+            i = torch.arange(self.rot_dim // 2, dtype=torch.float64)
+            self.inv_freq = torch.pow(torch.tensor(self.theta, dtype=torch.float64),
+                                      -(2.0 * i) / float(self.rot_dim)).to(torch.float32)
+            return
         i = torch.arange(self.rot_dim // 2, dtype=torch.float32)
         self.inv_freq = torch.pow(torch.tensor(self.theta, dtype=torch.float32),
                                   -(2.0 * i) / float(self.rot_dim))
