@@ -69,11 +69,14 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 // tile index i (absolute index key0 + i) counts for row r iff lo[r] <= key0 + i <= hi[r].
 // m, l: running maximum (log2 domain) and this thread's share of the running sum per row.
 // CAPPED: scores are soft-capped, cap * tanh(s * scale / cap), with cap_log2 = cap * log2(e).
-template <int NKT, bool MASKED = true, bool CAPPED = false>
+// BIASED: row r's scores are multiplied by rs[r] (a query temperature: the factor of q taken out of the dot product)
+// and sl[r] * (hi[r] - key) is taken off them (a bias by distance; sl = slope * log2(e), hi[r] = the row's position).
+template <int NKT, bool MASKED = true, bool CAPPED = false, bool BIASED = false>
 __device__ __forceinline__ void attend_tile(const unsigned (&qf)[KS][4], unsigned k_s, unsigned v_s, int key0,
                                             const int (&lo)[2], const int (&hi)[2], float scale_log2,
                                             float (&o)[DN][4], float (&m)[2], float (&l)[2], int lane,
-                                            float cap_log2 = 0.f) {
+                                            float cap_log2 = 0.f, const float* rs = nullptr, const float* sl = nullptr,
+                                            unsigned v_shift = 0) {
   const int c = lane & 3;
   float s[NKT][4];
 #pragma unroll
@@ -100,7 +103,9 @@ __device__ __forceinline__ void attend_tile(const unsigned (&qf)[KS][4], unsigne
       int key = key0 + n * 8 + 2 * c + (e & 1);
       int r = e >> 1;
       float sc = s[n][e] * scale_log2;
+      if (BIASED) sc *= rs[r];
       if (CAPPED) sc = cap_log2 * tanhf(sc / cap_log2);
+      if (BIASED) sc -= sl[r] * (float)(hi[r] - key);
       float v = (!MASKED || (key >= lo[r] && key <= hi[r])) ? sc : -INFINITY;
       s[n][e] = v;
       mx[r] = fmaxf(mx[r], v);
@@ -273,12 +278,15 @@ struct AttnArgs {
   int ldq, chunk, ldg;
   float cap_log2;
   const float* gate;
+  // slopes [H] of a bias by distance (null: none); a query temperature 1 + qt_coef ln(floor((p + 1) / qt_every) + 1)
+  // (qt_every 0: none); kv_planes: 2 = keys then values in a page-layer record, 1 = the values are the keys
+  const float* slopes; float qt_coef; int qt_every, kv_planes;
 };
 
 __device__ __forceinline__ const bf16* key_row(const AttnArgs& a, const int* bt, int g, int key) {
   int lp = key / a.page_tokens;
   int page = max(bt[lp], 0);                 // an unmapped entry (-1) must never become an address: page 0 is read instead
-  return a.pool + ((((size_t)page * a.layers_in_group + a.layer) * 2) * a.G + g) * ((size_t)a.page_tokens * HD)
+  return a.pool + ((((size_t)page * a.layers_in_group + a.layer) * a.kv_planes) * a.G + g) * ((size_t)a.page_tokens * HD)
          + (size_t)(key - lp * a.page_tokens) * HD;
 }
 
@@ -303,6 +311,8 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(AttnAr
   const int* bt = a.block_table + (size_t)a.row_slot[row_begin] * a.max_pages;
   pdl_wait(); FELLM_TRACE_WAITED();
   const unsigned s_base = (unsigned)__cvta_generic_to_shared(smem);
+  const bool biased = a.slopes != nullptr || a.qt_every > 0;
+  const bool v_is_k = a.kv_planes == 1;
   constexpr int TILE_B = PF_TK * ROWB;                         // bytes of one K (or V) tile
 
   // Causal work grows with the block's position: a CTA takes block bx and then its mirror
@@ -316,6 +326,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(AttnAr
 
     // this thread's two rows: (token, head of the group)
     int tok[2], hr[2], lo[2], hi[2];
+    float rs[2] = {1.f, 1.f}, sl[2] = {0.f, 0.f};
     bool valid[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -327,6 +338,10 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(AttnAr
       lo[r] = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
       if (a.chunk > 0) lo[r] = max(lo[r], (pos / a.chunk) * a.chunk);
       if (!valid[r]) lo[r] = 1 << 30;
+      if (biased && valid[r]) {
+        if (a.qt_every > 0) rs[r] = 1.0f + a.qt_coef * logf((float)((pos + 1) / a.qt_every + 1));
+        if (a.slopes) sl[r] = a.slopes[g * R + hr[r]] * 1.4426950408889634f;
+      }
     }
     unsigned qf[KS][4];
     load_q(qf, [&](int i) -> const bf16* {
@@ -353,10 +368,10 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(AttnAr
           if (key <= k_last) {
             const bf16* kp = key_row(a, bt, g, key) + ch * 8;
             cp_async16(ks + tile_off(row, ch), kp);
-            cp_async16(vs + tile_off(row, ch), kp + (size_t)a.G * a.page_tokens * HD);
+            if (!v_is_k) cp_async16(vs + tile_off(row, ch), kp + (size_t)a.G * a.page_tokens * HD);
           } else {                       // past the last key: zeros, so that 0 * V stays 0
             st_shared_zero16(ks + tile_off(row, ch));
-            st_shared_zero16(vs + tile_off(row, ch));
+            if (!v_is_k) st_shared_zero16(vs + tile_off(row, ch));
           }
         }
       }
@@ -368,12 +383,15 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(AttnAr
       issue(j + 1);
       cp_async_wait<1>();
       __syncthreads();
-      unsigned ks = s_base + (j % PF_STAGES) * 2 * TILE_B, vs = ks + TILE_B;
+      unsigned ks = s_base + (j % PF_STAGES) * 2 * TILE_B, vs = v_is_k ? ks : ks + TILE_B;
       int key0 = k_first + j * PF_TK;
       // a warp whose rows all end before this tile has nothing to add (warp-uniform test)
       int warp_hi = pos0 + min(n_tok - 1, (warp * 16 + 15) / R);
       if (key0 <= warp_hi && warp * 16 < n_tok * R) {
-        if (a.cap_log2 > 0.f) attend_tile<PF_TK / 8, true, true>(qf, ks, vs, key0, lo, hi, a.scale_log2, o, m, l, lane, a.cap_log2);
+        if (biased) {
+          if (a.cap_log2 > 0.f) attend_tile<PF_TK / 8, true, true, true>(qf, ks, vs, key0, lo, hi, a.scale_log2, o, m, l, lane, a.cap_log2, rs, sl);
+          else attend_tile<PF_TK / 8, true, false, true>(qf, ks, vs, key0, lo, hi, a.scale_log2, o, m, l, lane, 0.f, rs, sl);
+        } else if (a.cap_log2 > 0.f) attend_tile<PF_TK / 8, true, true>(qf, ks, vs, key0, lo, hi, a.scale_log2, o, m, l, lane, a.cap_log2);
         else attend_tile<PF_TK / 8>(qf, ks, vs, key0, lo, hi, a.scale_log2, o, m, l, lane);
       }
       __syncthreads();                                         // the stage is refilled by the next issue
@@ -1064,6 +1082,7 @@ static int fill_args(AttnArgs& a, const void* q, const void* pool, const int* bl
   a.scale_log2 = scale * 1.4426950408889634f;
   a.item_start = nullptr; a.scratch = nullptr; a.counters = nullptr; a.split_len = 1; a.max_splits = 1; a.n_items = 0;
   a.ldq = H * HD; a.chunk = 0; a.ldg = 0; a.cap_log2 = 0.f; a.gate = nullptr;
+  a.slopes = nullptr; a.qt_coef = 0.f; a.qt_every = 0; a.kv_planes = 2;
   return 0;
 }
 
@@ -1087,11 +1106,31 @@ FELLM_API int fellm_attn_prefill_mma(const void* q, const void* pool, const int*
                                         0, 0.f, nullptr, 0, stream);
 }
 
+// The same with a bias by distance (slopes float32 [H], null: none), a query temperature (qt_every 0: none) and values
+// that are the keys (v_is_k: a page-layer record is the keys [G][page_tokens][hd] alone).
+FELLM_API int fellm_attn_prefill_mma_biased(const void* q, int ldq, const void* pool, const int* block_table, int max_pages,
+                                            const int* positions, const int* row_slot, const int* item_start, int n_items,
+                                            int max_item_rows, void* out, int T, int H, int G, int hd, int page_tokens,
+                                            int layer, int layers_in_group, float scale, int window, int chunk,
+                                            float softcap, const float* gate, int ldg, const float* slopes, float qt_coef,
+                                            int qt_every, int v_is_k, cudaStream_t stream);
+
 FELLM_API int fellm_attn_prefill_mma_general(const void* q, int ldq, const void* pool, const int* block_table, int max_pages,
                                              const int* positions, const int* row_slot, const int* item_start, int n_items,
                                              int max_item_rows, void* out, int T, int H, int G, int hd, int page_tokens,
                                              int layer, int layers_in_group, float scale, int window, int chunk,
                                              float softcap, const float* gate, int ldg, cudaStream_t stream) {
+  return fellm_attn_prefill_mma_biased(q, ldq, pool, block_table, max_pages, positions, row_slot, item_start, n_items,
+                                       max_item_rows, out, T, H, G, hd, page_tokens, layer, layers_in_group, scale, window,
+                                       chunk, softcap, gate, ldg, nullptr, 0.f, 0, 0, stream);
+}
+
+FELLM_API int fellm_attn_prefill_mma_biased(const void* q, int ldq, const void* pool, const int* block_table, int max_pages,
+                                            const int* positions, const int* row_slot, const int* item_start, int n_items,
+                                            int max_item_rows, void* out, int T, int H, int G, int hd, int page_tokens,
+                                            int layer, int layers_in_group, float scale, int window, int chunk,
+                                            float softcap, const float* gate, int ldg, const float* slopes, float qt_coef,
+                                            int qt_every, int v_is_k, cudaStream_t stream) {
   if (T <= 0 || n_items <= 0) return 0;
   AttnArgs a;
   int e = fill_args(a, q, pool, block_table, max_pages, positions, row_slot, out, T, H, G, hd, page_tokens, layer,
@@ -1100,6 +1139,8 @@ FELLM_API int fellm_attn_prefill_mma_general(const void* q, int ldq, const void*
   if (!item_start) return FELLM_ERR_ARG;
   if (ldq < H * hd || (ldq & 1) || chunk < 0 || softcap < 0.f) return FELLM_ERR_ARG;
   a.ldq = ldq; a.chunk = chunk; a.cap_log2 = softcap * 1.4426950408889634f; a.gate = gate; a.ldg = ldg;
+  if (qt_every < 0) return FELLM_ERR_ARG;
+  a.slopes = slopes; a.qt_coef = qt_coef; a.qt_every = qt_every; a.kv_planes = v_is_k ? 1 : 2;
   int R = H / G;
   if (R > PF_WARPS * 16) return FELLM_ERR_SIZE;
   a.item_start = item_start; a.n_items = n_items;

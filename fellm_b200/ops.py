@@ -1334,13 +1334,23 @@ def attention_prefill(q, pool, block_table, positions, row_slot, item_start, n_i
 
 
 def attention_prefill_general(qkv, H, pool, block_table, positions, row_slot, item_start, n_items, max_item_rows, layer,
-                              scale, *, window=None, chunk=None, softcap=None, gate=None, out=None):
+                              scale, *, window=None, chunk=None, softcap=None, gate=None, slopes=None, q_temp=None,
+                              values_are_keys=None, out=None):
     """Portions of prompts on tensor cores (bfloat16; keys and values of one size, the one the library is compiled
     for) with the part's soft cap, chunks and gate: q is read in place from rows [T, >= H*hd] (heads at column 0),
-    gate float32 [T, >= H].  pool [pages, layers, 2, G, page_tokens, hd]."""
-    _dev(qkv, pool, block_table, positions, row_slot, item_start, gate)
+    gate float32 [T, >= H].  pool [pages, layers, 2, G, page_tokens, hd].  slopes float32 [H] and q_temp = (coef,
+    every) as in paged_attention_general.  values_are_keys = (G, page_tokens, hd): the pool is [pages, layers,
+    G * page_tokens * hd], keys alone, read as the values too."""
+    _dev(qkv, pool, block_table, positions, row_slot, item_start, gate, slopes)
     T = qkv.shape[0]
-    G, page_tokens, hd = pool.shape[3], pool.shape[4], pool.shape[5]
+    if values_are_keys:
+        G, page_tokens, hd = values_are_keys
+        assert pool.dim() == 3 and pool.shape[2] == G * page_tokens * hd
+    else:
+        G, page_tokens, hd = pool.shape[3], pool.shape[4], pool.shape[5]
+    if slopes is not None:
+        assert slopes.dtype == torch.float32 and slopes.numel() == H and slopes.is_contiguous()
+    qt_coef, qt_every = q_temp if q_temp else (0.0, 0)
     if qkv.dtype != torch.bfloat16 or pool.dtype != torch.bfloat16 or hd % 16 or not 16 <= hd <= 256 or H % G or H // G > 64:
         raise KernelError("attention_prefill_general takes bfloat16, head sizes of a multiple of 16 in 16..256, up to 64 heads a kv head")
     assert qkv.stride(1) == 1 and qkv.stride(0) % 2 == 0 and pool.is_contiguous()
@@ -1349,13 +1359,13 @@ def attention_prefill_general(qkv, H, pool, block_table, positions, row_slot, it
         assert gate.dtype == torch.float32 and gate.stride(1) == 1
     if out is None:
         out = torch.empty((T, H * hd), dtype=torch.bfloat16, device=qkv.device)
-    f = _fn("attention_mma", "fellm_attn_prefill_mma_general",
+    f = _fn("attention_mma", "fellm_attn_prefill_mma_biased",
             [_c_p, _c_int, _c_p, _c_p, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int,
-             _c_int, _c_int, _c_f, _c_int, _c_int, _c_f, _c_p, _c_int, _c_p], defines={"HD": hd})
+             _c_int, _c_int, _c_f, _c_int, _c_int, _c_f, _c_p, _c_int, _c_p, _c_f, _c_int, _c_int, _c_p], defines={"HD": hd})
     _check(f(_p(qkv), qkv.stride(0), _p(pool), _p(block_table), block_table.shape[1], _p(positions), _p(row_slot),
              _p(item_start), n_items, max_item_rows, _p(out), T, H, G, hd, page_tokens, layer, pool.shape[1], float(scale),
              int(window or 0), int(chunk or 0), float(softcap or 0.0), _p(gate), gate.stride(0) if gate is not None else 0,
-             _stream()), "attention_prefill_general")
+             _p(slopes), float(qt_coef), int(qt_every), int(bool(values_are_keys)), _stream()), "attention_prefill_general")
     return out
 
 

@@ -50,7 +50,7 @@ class Attention(Mixer):
         # what the kernels need of a position part: inv_freq (float32 [rot_dim/2], or None for no
         # rotation), pairing, rot_dim <= head_dim (the rotated leading elements of a head)
         self.rot_dim = self.hd if self.position.inv_freq is None else int(getattr(self.position, "rot_dim", self.hd))
-        if self.rot_dim % 2 or not 2 <= self.rot_dim <= self.hd:
+        if self.position.inv_freq is not None and (self.rot_dim % 2 or not 2 <= self.rot_dim <= self.hd):
             raise ConfigError(f"attention: rotary dimension {self.rot_dim} must be even and within head_dim {self.hd}")
         if self.position.inv_freq is not None and self.position.inv_freq.numel() != self.rot_dim // 2:
             raise ConfigError(f"attention: the position part gives {self.position.inv_freq.numel()} frequencies "
@@ -167,12 +167,13 @@ class Attention(Mixer):
             vd = 0              # nothing is kept beside the keys; the read-out has their size
         ops.kv_write(qkv, H * hd, (H + G) * hd, cache.pool, cache.block_table, ctx.positions, ctx.row_slot, cache.layer,
                      cache.page_tokens, G, hd, vd, status=ctx.status)
-        plain = not (self.values_are_keys or self.slope_exp is not None or self.q_temp)
-        if plain and self._on_tensor_cores(qkv) and not ctx.all_single:
+        if self._on_tensor_cores(qkv) and not ctx.all_single:
             # portions of prompts: the tensor-core kernel (keys and values of one size)
             a = ops.attention_prefill_general(qkv, H, cache.pool, cache.block_table, ctx.positions, ctx.row_slot,
                                               ctx.item_start, ctx.n_items, ctx.max_item_rows, cache.layer, self.scale,
-                                              window=self.window, chunk=self.chunk, softcap=self.softcap, gate=gate)
+                                              window=self.window, chunk=self.chunk, softcap=self.softcap, gate=gate,
+                                              slopes=self.w.get("slopes"), q_temp=self.q_temp,
+                                              values_are_keys=(G, cache.page_tokens, hd) if self.values_are_keys else None)
         else:
             a = ops.paged_attention_general(qkv, H, hd, vd, cache.pool, cache.block_table, ctx.positions, ctx.row_slot,
                                             cache.layer, cache.page_tokens, G, self.scale, window=self.window,
