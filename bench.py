@@ -332,6 +332,26 @@ def robazen_config(width, ff, layers, vocab):
                 layers=[dict(type=kinds[i % 4][0], mixer=kinds[i % 4][1], mlp=dict(ff=ff, kind="dense")) for i in range(layers)])
 
 
+def samusun_config(width, ff, layers, vocab):
+    """A Samusun model of real-looking layers at this width: attention layers with heads of 64 (four per key head; the
+    keys are the values) and a window of 1,024 positions, and a retention layer with heads of 128 x 128; feed-forwards by
+    turns dense (`ff`) and routed (8 experts of ff / 2, two a token: the same work a token, four times the weights);
+    every layer is mixer and feed-forward side by side behind one norm; no loop."""
+    H = width // 64
+    att = dict(dim=64, heads=H, kv_heads=max(H // 4, 1), mask=dict(size=1024), q_temp=dict(coef=0.3, every=256),
+               scale=0.125, vdim=64)
+    R = max(width // 128, 1)
+    ret = dict(decay=[1.0 - 2.0 ** -(5 + 3 * h / R) for h in range(R)], dim=128, heads=R, rot=dict(base=10000.0, dims=64), vdim=128)
+    dense = dict(ff=ff, kind="dense")
+    moe = dict(expert=dict(ff=ff // 2), kind="moe", router=dict(experts=8, top=2))
+    kinds = [("attention", att, dense), ("retention", ret, moe), ("attention", att, dense), ("attention", att, moe)]
+    return dict(architecture="Samusun", embedding=dict(scale=1.0), logit_scale=1.0, logit_softcap=30.0, vocab=vocab, width=width,
+                norm=dict(eps=1e-5), layers=[dict(type=kinds[i % 4][0], mixer=kinds[i % 4][1], mlp=kinds[i % 4][2]) for i in range(layers)])
+
+
+DESIGNS = {"robazen": robazen_config, "samusun": samusun_config}
+
+
 def run_design(design, shapes, layers, batches, steps, warmup):
     """Prefill and decode of the new design beside the LFM2 model of the same width, depth, feed-forward and
     vocabulary (the closest model the engine has): random weights, the same measurements as the headline's."""
@@ -347,7 +367,7 @@ def run_design(design, shapes, layers, batches, steps, warmup):
         lfm2["block_auto_adjust_ff_dim"] = False
         width, ff, vocab = lfm2["hidden_size"], lfm2["block_ff_dim"], lfm2["vocab_size"]
         row = {}
-        for name, cfg in (("robazen", robazen_config(width, ff, layers, vocab)), ("lfm2", lfm2)):
+        for name, cfg in ((design, DESIGNS[design](width, ff, layers, vocab)), ("lfm2", lfm2)):
             ctx_end = PROMPT + warmup + steps + 80
             opts = EngineOptions(dtype="bfloat16", n_ctx=ctx_end, ctx_past_model=True, n_batch=4096, n_ubatch=2048,
                                  page_tokens=64, max_requests=max(batches), max_tokens=max(batches) * ctx_end, cuda_graphs=True)
@@ -517,7 +537,7 @@ def main():
                     help="with FELLM_B200_TRACE=1: write the kernel timeline of one decode step (--batch requests, or with --only prefill of one prefill step; "
                          "--context tokens each) to FILE and stop; not a bench value")
     ap.add_argument("--context", type=int, default=PROMPT)
-    ap.add_argument("--design", choices=["robazen"], default=None,
+    ap.add_argument("--design", choices=sorted(DESIGNS), default=None,
                     help="prefill and decode throughput of this design at a few real-looking sizes beside the LFM2 model of "
                          "equal width, depth and feed-forward (--layers layers, default 8; --steps decode steps, default 64); "
                          "prints one line of its own and leaves the headline measurement alone")
