@@ -100,6 +100,9 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, float* v) {
 struct UmmaArgs {
   const float* bias; void* out; int* status;
   int M, N, K, ldo;
+  // grouped form (gemm_umma_kernel<.., true>): row tile r of A is rows g_table[3r + 1] .. + g_table[3r + 2] and is
+  // multiplied by the matrix of group g_table[3r], whose rows start at g_table[3r] * g_wrows of W; *g_tiles row tiles
+  const int* g_table; const int* g_tiles; int g_wrows;
 };
 
 // One 32-column chunk of an output row: v[j] is C[m][n + j].
@@ -160,7 +163,7 @@ __device__ __forceinline__ void store_chunk(const UmmaArgs& a, float* v, int m, 
 // Persistent: a CTA walks over output tiles t = blockIdx.x, + gridDim.x, ... (tiles that follow one another share
 // their weight tile).  Two accumulators in tensor memory: while the epilogue warps read tile i out of one, the MMA
 // thread fills the other with tile i+1, and the TMA thread is already fetching operands further ahead.
-template <int EPI, int BN>
+template <int EPI, int BN, bool GROUPED = false>
 __global__ void __launch_bounds__(UM_THREADS)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, UmmaArgs a) {
   FELLM_TRACE_SCOPE(TRACE_GEMM_UMMA);
@@ -175,7 +178,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const unsigned full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
   const unsigned accfull0 = smem_u32(&bars[2 * STAGES]), accempty0 = smem_u32(&bars[2 * STAGES + 2]);
   const int k_blocks = (a.K + UM_BK - 1) / UM_BK;
-  const int m_tiles = (a.M + UM_BM - 1) / UM_BM, n_tiles = (a.N + BN - 1) / BN, total = m_tiles * n_tiles;
+  const int n_tiles = (a.N + BN - 1) / BN;
+  int m_tiles = (a.M + UM_BM - 1) / UM_BM;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
@@ -192,20 +196,30 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const unsigned tmem_base = tmem_base_s;
   pdl_launch_dependents();
   pdl_wait(); FELLM_TRACE_WAITED();                        // A is the output of the kernel before this one
+  if (GROUPED) m_tiles = *a.g_tiles;                       // (written on the device by a kernel before this one)
+  const int total = m_tiles * n_tiles;
+  // tile t: its first row of A, its first row of W, its first output column, and how many of its 128 rows count
+  auto coords = [&](int t, int& m0, int& w0, int& n0, int& rows) {
+    const int rt = t % m_tiles;
+    n0 = (t / m_tiles) * BN;
+    if (GROUPED) { m0 = a.g_table[3 * rt + 1]; rows = a.g_table[3 * rt + 2]; w0 = a.g_table[3 * rt] * a.g_wrows + n0; }
+    else { m0 = rt * UM_BM; rows = a.M - m0; w0 = n0; }
+  };
 
   if (warp == 0) {
     if (lane == 0) {
       unsigned it = 0;               // k-blocks issued so far, over all tiles: stage = it % STAGES
       bool ok = true;
       for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
-        const int m0 = (t % m_tiles) * UM_BM, n0 = (t / m_tiles) * BN;
+        int m0, w0, n0, rows;
+        coords(t, m0, w0, n0, rows);
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           int s = it % STAGES;
           if (it >= STAGES && !mbar_wait(empty0 + 8 * s, (it / STAGES - 1) & 1, a.status, 101)) { ok = false; break; }
           unsigned dst = tiles + s * STAGE_BYTES;
           mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
           tma_load_2d(dst, &map_a, kb * UM_BK, m0, full0 + 8 * s);
-          tma_load_2d(dst + UM_BM * UM_BK * 2, &map_w, kb * UM_BK, n0, full0 + 8 * s);
+          tma_load_2d(dst + UM_BM * UM_BK * 2, &map_w, kb * UM_BK, w0, full0 + 8 * s);
         }
       }
     }
@@ -242,8 +256,10 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     unsigned use = 0;
     for (int t = blockIdx.x; t < total; t += gridDim.x, ++use) {
       const unsigned acc = use & 1;
-      const int m0 = (t % m_tiles) * UM_BM, n0 = (t / m_tiles) * BN;
+      int m0, w0, n0, rows;
+      coords(t, m0, w0, n0, rows);
       const int m = m0 + q * 32 + lane;
+      const bool row_ok = q * 32 + lane < rows;
       // += residual: what out holds in this thread's two chunks is fetched while the MMAs of the
       // tile still run (nothing else writes these elements during the launch)
       constexpr int CHUNKS = BN / 2 / 32;
@@ -253,7 +269,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
       for (int ch = 0; ch < CHUNKS; ++ch) {
         const int n = n0 + half * (BN / 2) + ch * 32;
-        res_ok[ch] = EPI == EPI_ACC && ch < PRE && m < a.M && n + 32 <= a.N && (a.ldo % 4) == 0;
+        res_ok[ch] = EPI == EPI_ACC && ch < PRE && row_ok && n + 32 <= a.N && (a.ldo % 4) == 0;
         if (EPI == EPI_ACC && res_ok[ch]) {
           const float4* src = (const float4*)((const float*)a.out + (size_t)m * a.ldo + n);
 #pragma unroll
@@ -267,7 +283,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const int c0 = half * (BN / 2) + ch * 32;
         float v[32];
         tmem_ld32(tmem_base + ((unsigned)(q * 32) << 16) + acc * BN + (unsigned)c0, v);      // whole warp, also for rows past M
-        if (m < a.M && n0 + c0 < a.N) store_chunk<EPI>(a, v, m, n0 + c0, (EPI == EPI_ACC && res_ok[ch]) ? res[ch < PRE ? ch : 0] : nullptr);
+        if (row_ok && n0 + c0 < a.N) store_chunk<EPI>(a, v, m, n0 + c0, (EPI == EPI_ACC && res_ok[ch]) ? res[ch < PRE ? ch : 0] : nullptr);
       }
       // this warp has read its part of the accumulator: one of the eight arrivals that free it
       asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -655,6 +671,17 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mw, const UmmaArgs& 
 }
 
 template <int EPI, int BN>
+static int launch_grouped(const CUtensorMap& ma, const CUtensorMap& mw, const UmmaArgs& a, int max_tiles, cudaStream_t stream) {
+  size_t smem = (size_t)(BN == 256 ? 4 : UM_STAGES) * (UM_BM + BN) * UM_BK * 2 + 1024;
+  auto kern = gemm_umma_kernel<EPI, BN, true>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  const int n_sm = fellm_sm_count();
+  long long total = (long long)ceil_div(a.N, BN) * max_tiles;
+  return launch_k_class(0, kern, dim3((unsigned)(total < n_sm ? total : n_sm), 1, 1), dim3(UM_THREADS, 1, 1), smem, stream, 1, ma, mw, a);
+}
+
+template <int EPI, int BN>
 static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, const UmmaArgs& a, cudaStream_t stream) {
   size_t smem = (size_t)(BN == 256 ? 6 : 8) * (UM_BM + BN / 2) * UM_BK * 2 + 1024;
   auto kern = gemm_umma_pair_kernel<EPI, BN>;
@@ -715,6 +742,7 @@ FELLM_API int fellm_gemm_umma(const void* A, const void* W, const float* bias, v
   int e = make_map(&ma, A, M, K, lda, UM_BM);
   if (e) return e;
   UmmaArgs a; a.bias = bias; a.out = out; a.status = status; a.M = M; a.N = N; a.K = K; a.ldo = ldo;
+  a.g_table = nullptr; a.g_tiles = nullptr; a.g_wrows = 0;
   // few tiles and a long K (a few hundred rows, a narrow N): two CTAs a 128 x 128 tile, half of K each
   static int ksplit = -1;
   if (ksplit < 0) { const char* ev = getenv("FELLM_B200_UMMA_KSPLIT"); ksplit = (ev && ev[0] == '0') ? 0 : 1; }
@@ -751,6 +779,31 @@ FELLM_API int fellm_gemm_umma(const void* A, const void* W, const float* bias, v
     case EPI_F32: return wide ? launch<EPI_F32, 256>(ma, mw, a, stream) : launch<EPI_F32, 128>(ma, mw, a, stream);
     default: return FELLM_ERR_ARG;
   }
+}
+
+// Grouped product (routed experts): A [P, K] holds the rows of all groups, sorted by group; W [groups * rows_per_group, K]
+// the groups' matrices one behind the other; table [max_tiles][3] = (group, first row, rows <= 128) and *n_tiles are
+// written on the device by the kernel that sorted the rows.  out [P, N] (EPI_F32) or [P, N / 2] (EPI_SWIGLU, each
+// group's gate and up rows interleaved in blocks of 8) in the order of A's rows.  A tile's TMA box reads the rows
+// behind its own too (the next group's, or zeros past P); their sums are computed and never stored.
+FELLM_API int fellm_gemm_umma_grouped(const void* A, const void* W, void* out, int epi, int P, int N, int K, int groups,
+                                      int lda, int ldo, const int* table, const int* n_tiles, int max_tiles, int* status,
+                                      cudaStream_t stream) {
+  if (P <= 0 || N <= 0 || max_tiles <= 0) return 0;
+  if (!A || !W || !out || !table || !n_tiles || K <= 0 || groups < 1) return FELLM_ERR_ARG;
+  if ((K % 8) || (lda % 8) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return FELLM_ERR_SIZE;
+  if (epi == EPI_SWIGLU && ((N % 16) || (ldo % 8))) return FELLM_ERR_SIZE;
+  if (epi != EPI_SWIGLU && epi != EPI_F32) return FELLM_ERR_ARG;
+  const bool wide = N >= 1024;
+  CUtensorMap ma, mw;
+  int e = make_map(&ma, A, P, K, lda, UM_BM);
+  if (e) return e;
+  e = make_map(&mw, W, groups * N, K, K, wide ? 256 : 128);
+  if (e) return e;
+  UmmaArgs a; a.bias = nullptr; a.out = out; a.status = status; a.M = P; a.N = N; a.K = K; a.ldo = ldo;
+  a.g_table = table; a.g_tiles = n_tiles; a.g_wrows = N;
+  if (epi == EPI_SWIGLU) return wide ? launch_grouped<EPI_SWIGLU, 256>(ma, mw, a, max_tiles, stream) : launch_grouped<EPI_SWIGLU, 128>(ma, mw, a, max_tiles, stream);
+  return wide ? launch_grouped<EPI_F32, 256>(ma, mw, a, max_tiles, stream) : launch_grouped<EPI_F32, 128>(ma, mw, a, max_tiles, stream);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -19,13 +19,8 @@
 #define PLAN_TILE 1024
 
 // ---------------------------------------------------------------- routing
-// One warp per token.  logits float32 [T, ld]; idx [T, top] int32; w [T, top] float32.
-__global__ void __launch_bounds__(128)
-moe_route_kernel(const float* __restrict__ logits, int ld, int T, int E, int top, int renorm,
-                 int* __restrict__ idx, float* __restrict__ w) {
-  const int warp = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (warp >= T) return;
-  const float* z = logits + (size_t)warp * ld;
+// One warp: softmax over z[0..E) in float32, the `top` largest (ties: the lower expert) into idx / w.
+__device__ __forceinline__ void route_warp(const float* z, int E, int top, int renorm, int* idx, float* w, int lane) {
   float m = -INFINITY;
   for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
   m = warp_max(m);
@@ -60,10 +55,19 @@ moe_route_kernel(const float* __restrict__ logits, int ld, int T, int E, int top
 #pragma unroll
     for (int c = 0; c < MOE_MAX_TOP; ++c) {
       if (c >= top) break;
-      idx[(size_t)warp * top + c] = taken[c];
-      w[(size_t)warp * top + c] = renorm ? tw[c] / chosen : tw[c];
+      idx[c] = taken[c];
+      w[c] = renorm ? tw[c] / chosen : tw[c];
     }
   }
+}
+
+// One warp per token.  logits float32 [T, ld]; idx [T, top] int32; w [T, top] float32.
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ logits, int ld, int T, int E, int top, int renorm,
+                 int* __restrict__ idx, float* __restrict__ w) {
+  const int warp = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (warp >= T) return;
+  route_warp(logits + (size_t)warp * ld, E, top, renorm, idx + (size_t)warp * top, w + (size_t)warp * top, lane);
 }
 
 FELLM_API int fellm_moe_route(const float* logits, int ld, int T, int E, int top, int renorm, int* idx, float* w,
@@ -72,6 +76,41 @@ FELLM_API int fellm_moe_route(const float* logits, int ld, int T, int E, int top
   if (E < 1 || top < 1 || top > E || top > MOE_MAX_TOP) return FELLM_ERR_SIZE;
   if (!logits || !idx || !w) return FELLM_ERR_ARG;
   moe_route_kernel<<<(T + 3) / 4, 128, 0, stream>>>(logits, ld, T, E, top, renorm, idx, w);
+  return launch_status();
+}
+
+// The router's product and the routing in one kernel: a block per token, its warps take the experts by turns
+// (z_e = sum_k h[k] Wr[e, k] in float32: a lane sums its share of k in order, the lanes are added by a butterfly: the
+// order depends on K alone), then the first warp routes.  h [T, ldh] and Wr [E, K] bfloat16 or float32.
+#define ROUTER_WARPS 4
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(ROUTER_WARPS * 32)
+moe_router_kernel(const TA* __restrict__ h, int ldh, const TW* __restrict__ Wr, int K, int E, int top, int renorm,
+                  int* __restrict__ idx, float* __restrict__ w) {
+  extern __shared__ float zs[];                 // [E]
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const TA* hr = h + (size_t)t * ldh;
+  for (int e = warp; e < E; e += ROUTER_WARPS) {
+    const TW* wr = Wr + (size_t)e * K;
+    float s = 0.f;
+    for (int k = lane; k < K; k += 32) s = fmaf(to_f(hr[k]), to_f(wr[k]), s);
+    s = warp_sum(s);
+    if (lane == 0) zs[e] = s;
+  }
+  __syncthreads();
+  if (warp == 0) route_warp(zs, E, top, renorm, idx + (size_t)t * top, w + (size_t)t * top, lane);
+}
+
+FELLM_API int fellm_moe_router(const void* h, int h_bf16, int ldh, const void* Wr, int w_bf16, int T, int K, int E, int top,
+                               int renorm, int* idx, float* w, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (E < 1 || top < 1 || top > E || top > MOE_MAX_TOP || (size_t)E * sizeof(float) > 48 * 1024) return FELLM_ERR_SIZE;
+  if (!h || !Wr || !idx || !w) return FELLM_ERR_ARG;
+  const size_t sh = (size_t)E * sizeof(float);
+#define ROUTER(TA_, TW_) moe_router_kernel<TA_, TW_><<<T, ROUTER_WARPS * 32, sh, stream>>>((const TA_*)h, ldh, (const TW_*)Wr, K, E, top, renorm, idx, w)
+  if (h_bf16) { if (w_bf16) ROUTER(bf16, bf16); else ROUTER(bf16, float); }
+  else { if (w_bf16) ROUTER(float, bf16); else ROUTER(float, float); }
+#undef ROUTER
   return launch_status();
 }
 
@@ -135,12 +174,55 @@ __global__ void moe_place_kernel(const int* __restrict__ idx, const int* __restr
   place_of[p] = place;
 }
 
+// Up to PLAN_TILE pairs (a decode step): count, scan and places in one block.
+__global__ void __launch_bounds__(PLAN_TILE)
+moe_plan_small_kernel(const int* __restrict__ idx, int P, int E, int BM, int* __restrict__ sorted, int* __restrict__ place_of,
+                      int* __restrict__ table, int* __restrict__ n_tiles) {
+  __shared__ int ex[PLAN_TILE];
+  extern __shared__ int sh[];            // [E] rows of an expert, then [E] its first row
+  int* rows = sh; int* first = sh + E;
+  const int p = threadIdx.x;
+  const int e = p < P ? idx[p] : -1;
+  ex[p] = e;
+  for (int i = p; i < E; i += PLAN_TILE) rows[i] = 0;
+  __syncthreads();
+  int r = 0;
+  if (e >= 0) {
+    for (int j = 0; j < p; ++j) r += ex[j] == e;
+    bool last = true;
+    for (int j = p + 1; j < P && last; ++j) last = ex[j] != e;
+    if (last) rows[e] = r + 1;
+  }
+  __syncthreads();
+  if (p == 0) {
+    int at = 0, tiles = 0;
+    for (int i = 0; i < E; ++i) {
+      first[i] = at;
+      for (int q = 0; q < rows[i]; q += BM, ++tiles) {
+        table[3 * tiles] = i; table[3 * tiles + 1] = at + q; table[3 * tiles + 2] = min(BM, rows[i] - q);
+      }
+      at += rows[i];
+    }
+    *n_tiles = tiles;
+  }
+  __syncthreads();
+  if (e >= 0) {
+    const int place = first[e] + r;
+    sorted[place] = p;
+    place_of[p] = place;
+  }
+}
+
 // scratch (int32): counts [tiles][E] | base [tiles][E] | rank [P]
 FELLM_API int fellm_moe_plan(const int* idx, int P, int E, int BM, int* scratch, int* sorted, int* place_of, int* table,
                              int* n_tiles, cudaStream_t stream) {
   if (P <= 0) return 0;
   if (E < 1 || BM < 1) return FELLM_ERR_SIZE;
   if (!idx || !scratch || !sorted || !place_of || !table || !n_tiles) return FELLM_ERR_ARG;
+  if (P <= PLAN_TILE && (size_t)2 * E * sizeof(int) <= 40 * 1024) {
+    moe_plan_small_kernel<<<1, PLAN_TILE, (size_t)2 * E * sizeof(int), stream>>>(idx, P, E, BM, sorted, place_of, table, n_tiles);
+    return launch_status();
+  }
   const int tiles = (P + PLAN_TILE - 1) / PLAN_TILE;
   int* counts = scratch; int* base = counts + (size_t)tiles * E; int* rank = base + (size_t)tiles * E;
   moe_count_kernel<<<tiles, PLAN_TILE, 0, stream>>>(idx, P, E, counts, rank);
@@ -154,15 +236,18 @@ FELLM_API int fellm_moe_plan(const int* idx, int P, int E, int BM, int* scratch,
 // ---------------------------------------------------------------- grouped products, float32 FMA
 // Every output is ONE chain of fused multiply-adds over k = 0..K-1: the 32-bit engine's product, and the bfloat16
 // engine's where the tensor-core kernel below does not take a size.
-// GATED: W[e] is [2N, K], gate rows first; the epilogue stores SiLU(gate) * up.  Rows of A: gather[row] / top when
-// gather is given (a pair's token), else the sorted row itself.
+// GATED: W[e] is [2N, K]; the epilogue stores SiLU(gate) * up.  inter = 0: the N gate rows first, then the N up
+// rows; inter = 1: blocks of 8 gate rows and 8 up rows by turns (the layout the tcgen05 product's epilogue reads).
+// Rows of A: gather[row] / top when gather is given (a pair's token), else the sorted row itself.
+__device__ __forceinline__ int gate_row(int n, int inter) { return inter ? ((n >> 3) << 4) + (n & 7) : n; }
+__device__ __forceinline__ int up_row(int n, int N, int inter) { return inter ? ((n >> 3) << 4) + 8 + (n & 7) : N + n; }
 #define FB 64
 #define FK 16
 template <typename TA, typename TW, typename TO, bool GATED>
 __global__ void __launch_bounds__(256)
 moe_gemm_fma_kernel(const TA* __restrict__ A, int lda, const int* __restrict__ gather, int top,
                     const TW* __restrict__ W, TO* __restrict__ C, int ldc, int N, int K,
-                    const int* __restrict__ table, const int* __restrict__ n_tiles) {
+                    const int* __restrict__ table, const int* __restrict__ n_tiles, int inter) {
   if ((int)blockIdx.x >= *n_tiles) return;
   __shared__ float As[FK][FB + 1];
   __shared__ float Ws[GATED ? 2 : 1][FK][FB + 1];
@@ -186,8 +271,8 @@ moe_gemm_fma_kernel(const TA* __restrict__ A, int lda, const int* __restrict__ g
       As[k][r] = (ar >= 0 && k0 + k < K) ? to_f(A[(size_t)ar * lda + k0 + k]) : 0.f;
       const int n = n0 + r;
       const bool ok = n < N && k0 + k < K;
-      Ws[0][k][r] = ok ? to_f(We[(size_t)n * K + k0 + k]) : 0.f;
-      if (GATED) Ws[1][k][r] = ok ? to_f(We[(size_t)(N + n) * K + k0 + k]) : 0.f;
+      Ws[0][k][r] = ok ? to_f(We[(size_t)(GATED ? gate_row(n, inter) : n) * K + k0 + k]) : 0.f;
+      if (GATED) Ws[1][k][r] = ok ? to_f(We[(size_t)up_row(n, N, inter) * K + k0 + k]) : 0.f;
     }
     __syncthreads();
 #pragma unroll
@@ -243,7 +328,7 @@ template <typename TO, bool GATED>
 __global__ void __launch_bounds__(128)
 moe_gemm_mma_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__ gather, int top,
                     const bf16* __restrict__ W, TO* __restrict__ C, int ldc, int N, int K,
-                    const int* __restrict__ table, const int* __restrict__ n_tiles) {
+                    const int* __restrict__ table, const int* __restrict__ n_tiles, int inter) {
   if ((int)blockIdx.x >= *n_tiles) return;
   __shared__ __align__(16) bf16 As[2][TB * TLD];
   __shared__ __align__(16) bf16 Ws[2][(GATED ? 2 : 1) * TB * TLD];
@@ -268,8 +353,8 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__
       if (ar >= 0 && k0 + kv < K) va = *(const uint4*)(A + (size_t)ar * lda + k0 + kv);
       const int n = n0 + r;
       if (n < N && k0 + kv < K) {
-        vw = *(const uint4*)(We + (size_t)n * K + k0 + kv);
-        if (GATED) vw2 = *(const uint4*)(We + (size_t)(N + n) * K + k0 + kv);
+        vw = *(const uint4*)(We + (size_t)(GATED ? gate_row(n, inter) : n) * K + k0 + kv);
+        if (GATED) vw2 = *(const uint4*)(We + (size_t)up_row(n, N, inter) * K + k0 + kv);
       }
       *(uint4*)(&As[buf][r * TLD + kv]) = va;
       *(uint4*)(&Ws[buf][r * TLD + kv]) = vw;
@@ -323,36 +408,125 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__
   }
 }
 
+// Few rows (a decode step): the product is bound by reading each chosen expert's matrix once.  A warp owns one
+// output column of a row tile (and, GATED, the column's up partner): it streams the column's weight row(s) 16 bytes a
+// lane at a time against up to VR rows of A at once (more rows: again, the weights then come from L1 / L2), the lanes'
+// sums are added by a butterfly.  bfloat16 only; K a multiple of 8.
+#define VW 8            // warps a block
+#define VR 4            // rows at once
+__device__ __forceinline__ void unpack8(const uint4& raw, float* f) {
+  const __nv_bfloat162* h = (const __nv_bfloat162*)&raw;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { float2 v = __bfloat1622float2(h[e]); f[2 * e] = v.x; f[2 * e + 1] = v.y; }
+}
+template <typename TO, bool GATED>
+__global__ void __launch_bounds__(VW * 32)
+moe_gemv_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__ gather, int top,
+                const bf16* __restrict__ W, TO* __restrict__ C, int ldc, int N, int K,
+                const int* __restrict__ table, const int* __restrict__ n_tiles, int inter) {
+  if ((int)blockIdx.x >= *n_tiles) return;
+  const int e = table[3 * blockIdx.x], row0 = table[3 * blockIdx.x + 1], rows = table[3 * blockIdx.x + 2];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.y * VW + warp;
+  if (n >= N) return;
+  const bf16* We = W + (size_t)e * (GATED ? 2 : 1) * N * K;
+  const bf16* wg = We + (size_t)(GATED ? gate_row(n, inter) : n) * K;
+  const bf16* wu = GATED ? We + (size_t)up_row(n, N, inter) * K : nullptr;
+  for (int r0 = 0; r0 < rows; r0 += VR) {
+    const bf16* ar[VR];
+#pragma unroll
+    for (int i = 0; i < VR; ++i) {
+      const int r = min(r0 + i, rows - 1);
+      ar[i] = A + (size_t)(gather ? gather[row0 + r] / top : row0 + r) * lda;
+    }
+    float sg[VR], su[VR];
+#pragma unroll
+    for (int i = 0; i < VR; ++i) sg[i] = su[i] = 0.f;
+    for (int k = lane * 8; k < K; k += 256) {
+      float fg[8], fu[8];
+      unpack8(*(const uint4*)(wg + k), fg);
+      if (GATED) unpack8(*(const uint4*)(wu + k), fu);
+#pragma unroll
+      for (int i = 0; i < VR; ++i) {
+        float fa[8];
+        unpack8(*(const uint4*)(ar[i] + k), fa);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { sg[i] = fmaf(fa[j], fg[j], sg[i]); if (GATED) su[i] = fmaf(fa[j], fu[j], su[i]); }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < VR; ++i) {
+      float g = warp_sum(sg[i]);
+      float u = GATED ? warp_sum(su[i]) : 0.f;
+      if (lane == 0 && r0 + i < rows) {
+        float v = g;
+        if (GATED) {
+          g = to_f(from_f<bf16>(g)); u = to_f(from_f<bf16>(u));
+          v = g / (1.0f + expf(-g)) * u;
+        }
+        C[(size_t)(row0 + r0 + i) * ldc + n] = from_f<TO>(v);
+      }
+    }
+  }
+}
+
 // A [*, lda] (bfloat16 or float32), W [E][(gated ? 2 : 1) * N][K] of the same kind; C [P, ldc]: bfloat16 or float32
 // when gated (the activation), float32 otherwise.  max_tiles: the table's capacity = the launch's first extent.
 FELLM_API int fellm_moe_gemm(const void* A, int a_bf16, int lda, const int* gather, int top, const void* W, int w_bf16,
                              void* C, int c_bf16, int ldc, int N, int K, int gated, const int* table, const int* n_tiles,
-                             int max_tiles, int use_mma, cudaStream_t stream) {
+                             int max_tiles, int use_mma, int inter, int few_rows, cudaStream_t stream) {
   if (max_tiles <= 0) return 0;
   if (N < 1 || K < 1 || top < 1) return FELLM_ERR_SIZE;
   if (!A || !W || !C || !table || !n_tiles) return FELLM_ERR_ARG;
   if (a_bf16 != w_bf16 || (!gated && c_bf16) || (gated && c_bf16 != a_bf16)) return FELLM_ERR_ARG;
   const bool mma = use_mma && a_bf16 && K % 8 == 0 && lda % 8 == 0 && ((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0;
+  if (mma && few_rows) {
+    dim3 grid(max_tiles, (N + VW - 1) / VW);
+    if (gated)
+      moe_gemv_kernel<bf16, true><<<grid, VW * 32, 0, stream>>>((const bf16*)A, lda, gather, top, (const bf16*)W, (bf16*)C, ldc, N, K, table, n_tiles, inter);
+    else
+      moe_gemv_kernel<float, false><<<grid, VW * 32, 0, stream>>>((const bf16*)A, lda, gather, top, (const bf16*)W, (float*)C, ldc, N, K, table, n_tiles, inter);
+    return launch_status();
+  }
   if (mma) {
     dim3 grid(max_tiles, (N + TB - 1) / TB);
     if (gated)
-      moe_gemm_mma_kernel<bf16, true><<<grid, 128, 0, stream>>>((const bf16*)A, lda, gather, top, (const bf16*)W, (bf16*)C, ldc, N, K, table, n_tiles);
+      moe_gemm_mma_kernel<bf16, true><<<grid, 128, 0, stream>>>((const bf16*)A, lda, gather, top, (const bf16*)W, (bf16*)C, ldc, N, K, table, n_tiles, inter);
     else
-      moe_gemm_mma_kernel<float, false><<<grid, 128, 0, stream>>>((const bf16*)A, lda, gather, top, (const bf16*)W, (float*)C, ldc, N, K, table, n_tiles);
+      moe_gemm_mma_kernel<float, false><<<grid, 128, 0, stream>>>((const bf16*)A, lda, gather, top, (const bf16*)W, (float*)C, ldc, N, K, table, n_tiles, inter);
     return launch_status();
   }
   dim3 grid(max_tiles, (N + FB - 1) / FB);
   if (a_bf16) {
     if (gated)
-      moe_gemm_fma_kernel<bf16, bf16, bf16, true><<<grid, 256, 0, stream>>>((const bf16*)A, lda, gather, top, (const bf16*)W, (bf16*)C, ldc, N, K, table, n_tiles);
+      moe_gemm_fma_kernel<bf16, bf16, bf16, true><<<grid, 256, 0, stream>>>((const bf16*)A, lda, gather, top, (const bf16*)W, (bf16*)C, ldc, N, K, table, n_tiles, inter);
     else
-      moe_gemm_fma_kernel<bf16, bf16, float, false><<<grid, 256, 0, stream>>>((const bf16*)A, lda, gather, top, (const bf16*)W, (float*)C, ldc, N, K, table, n_tiles);
+      moe_gemm_fma_kernel<bf16, bf16, float, false><<<grid, 256, 0, stream>>>((const bf16*)A, lda, gather, top, (const bf16*)W, (float*)C, ldc, N, K, table, n_tiles, inter);
   } else {
     if (gated)
-      moe_gemm_fma_kernel<float, float, float, true><<<grid, 256, 0, stream>>>((const float*)A, lda, gather, top, (const float*)W, (float*)C, ldc, N, K, table, n_tiles);
+      moe_gemm_fma_kernel<float, float, float, true><<<grid, 256, 0, stream>>>((const float*)A, lda, gather, top, (const float*)W, (float*)C, ldc, N, K, table, n_tiles, inter);
     else
-      moe_gemm_fma_kernel<float, float, float, false><<<grid, 256, 0, stream>>>((const float*)A, lda, gather, top, (const float*)W, (float*)C, ldc, N, K, table, n_tiles);
+      moe_gemm_fma_kernel<float, float, float, false><<<grid, 256, 0, stream>>>((const float*)A, lda, gather, top, (const float*)W, (float*)C, ldc, N, K, table, n_tiles, inter);
   }
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- rows in sorted order
+// out[r, :] = a[sorted[r] / top, :]   (bfloat16, K a multiple of 8: 16 bytes a thread): the input of the tcgen05
+// grouped product, whose TMA boxes want an expert's rows side by side.
+__global__ void moe_gather_kernel(const bf16* __restrict__ a, int lda, const int* __restrict__ sorted, int top,
+                                  bf16* __restrict__ out, int K) {
+  const int r = blockIdx.x;
+  const bf16* src = a + (size_t)(sorted[r] / top) * lda;
+  bf16* dst = out + (size_t)r * K;
+  for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) *(uint4*)(dst + k) = *(const uint4*)(src + k);
+}
+
+FELLM_API int fellm_moe_gather(const void* a, int lda, const int* sorted, int top, void* out, int P, int K, cudaStream_t stream) {
+  if (P <= 0) return 0;
+  if (!a || !sorted || !out) return FELLM_ERR_ARG;
+  if (K % 8 || lda % 8 || ((uintptr_t)a % 16) || ((uintptr_t)out % 16)) return FELLM_ERR_SIZE;
+  moe_gather_kernel<<<P, 128, 0, stream>>>((const bf16*)a, lda, sorted, top, (bf16*)out, K);
   return launch_status();
 }
 

@@ -520,10 +520,14 @@ def branch_combine(x, branches, weights, eps: float):
 
 # ------------------------------------------------------------------------------ routed experts
 
-MOE_ROW_TILE = 64            # rows of a tile of the grouped products (both kernels)
+MOE_ROW_TILE = 64            # rows of a tile of the grouped products on CUDA cores and mma.sync
+MOE_UMMA_ROW_TILE = 128      # ... of the tcgen05 grouped product
 MOE_PLAN_TILE = 1024
 MOE_MAX_TOP = 16
 MOE_MMA = os.environ.get("FELLM_B200_MOE_MMA", "1") != "0"
+MOE_UMMA = os.environ.get("FELLM_B200_MOE_UMMA", "1") != "0"
+MOE_UMMA_MIN_PAIRS = int(os.environ.get("FELLM_B200_MOE_UMMA_MIN_PAIRS", 256))     # fewer (token, choice) pairs: mma.sync tiles of 64 rows
+MOE_FEW_PAIRS = int(os.environ.get("FELLM_B200_MOE_FEW_PAIRS", 64))                # up to this many: a warp a column (weight streaming)
 
 
 def moe_route(logits, E: int, top: int, renormalize: bool = False):
@@ -541,13 +545,36 @@ def moe_route(logits, E: int, top: int, renormalize: bool = False):
     return idx, w
 
 
+def moe_router(h, w_router, top: int, renormalize: bool = False):
+    """The router's product and the routing in one launch: z = h W_router^T in float32 (h [T, K] and W_router [E, K]
+    bfloat16 or float32), then as moe_route.  Returns (idx int32 [T, top], w float32 [T, top])."""
+    _dev(h, w_router)
+    assert h.stride(1) == 1 and w_router.is_contiguous() and h.shape[1] == w_router.shape[1]
+    T, K = h.shape
+    E = w_router.shape[0]
+    if not 1 <= top <= min(E, MOE_MAX_TOP):
+        raise KernelError(f"moe_router: top {top} must be in 1..{min(E, MOE_MAX_TOP)}")
+    idx = torch.empty((T, top), dtype=torch.int32, device=h.device)
+    w = torch.empty((T, top), dtype=torch.float32, device=h.device)
+    f = _fn("moe", "fellm_moe_router", [_c_p, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p])
+    _check(f(_p(h), _is_bf16(h), h.stride(0), _p(w_router), _is_bf16(w_router), T, K, E, top, int(renormalize), _p(idx),
+             _p(w), _stream()), "moe_router")
+    return idx, w
+
+
 class MoePlan:
     """The (token, choice) pairs of a step sorted by expert: sorted[place] = pair, place_of[pair] = place, and the
-    table of row tiles (expert, first row, rows) with their count on the device; max_tiles bounds it on the host."""
-    __slots__ = ("sorted", "place_of", "table", "n_tiles", "max_tiles", "pairs", "top")
+    table of row tiles (expert, first row, rows <= row_tile) with their count on the device; max_tiles bounds it on
+    the host."""
+    __slots__ = ("sorted", "place_of", "table", "n_tiles", "max_tiles", "pairs", "top", "row_tile")
 
 
-def moe_plan(idx, E: int) -> MoePlan:
+def moe_row_tile(pairs: int, bf16: bool, K_ok: bool) -> int:
+    """Rows of a tile for a step of this many pairs: 128 where the tcgen05 grouped product takes the step."""
+    return MOE_UMMA_ROW_TILE if (bf16 and K_ok and MOE_UMMA and USE_UMMA and pairs >= MOE_UMMA_MIN_PAIRS) else MOE_ROW_TILE
+
+
+def moe_plan(idx, E: int, row_tile: int = MOE_ROW_TILE) -> MoePlan:
     _dev(idx)
     _i32(idx, "idx")
     assert idx.is_contiguous()
@@ -555,8 +582,8 @@ def moe_plan(idx, E: int) -> MoePlan:
     P = T * top
     tiles = -(-P // MOE_PLAN_TILE)
     plan = MoePlan()
-    plan.pairs, plan.top = P, top
-    plan.max_tiles = min(P, E) + P // MOE_ROW_TILE
+    plan.pairs, plan.top, plan.row_tile = P, top, row_tile
+    plan.max_tiles = min(P, E) + P // row_tile
     ints = torch.empty(2 * tiles * E + P + 2 * P + 3 * plan.max_tiles + 1, dtype=torch.int32, device=idx.device)
     at = 2 * tiles * E + P
     scratch = ints[:at]
@@ -564,26 +591,46 @@ def moe_plan(idx, E: int) -> MoePlan:
     plan.table = ints[at + 2 * P:at + 2 * P + 3 * plan.max_tiles]
     plan.n_tiles = ints[at + 2 * P + 3 * plan.max_tiles:]
     f = _fn("moe", "fellm_moe_plan", [_c_p, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p])
-    _check(f(_p(idx), P, E, MOE_ROW_TILE, _p(scratch), _p(plan.sorted), _p(plan.place_of), _p(plan.table),
+    _check(f(_p(idx), P, E, row_tile, _p(scratch), _p(plan.sorted), _p(plan.place_of), _p(plan.table),
              _p(plan.n_tiles), _stream()), "moe_plan")
     return plan
 
 
-def moe_gemm(a, w, plan: MoePlan, *, gated: bool, gather: bool, out_dtype=None):
+def moe_gemm(a, w, plan: MoePlan, *, gated: bool, gather: bool, interleaved: bool = False):
     """Grouped product over a plan's row tiles.  w [E, (2 if gated else 1) * N, K]; gather: row r of the result
     reads a[token of the pair sorted r] (a [T, K]); else a [P, K] is in sorted order.  gated: SiLU(gate) * up in
-    a's dtype; else float32.  Returns [P, N] in sorted order."""
+    a's dtype (w's rows: gate rows then up rows, or, interleaved, blocks of 8 gate and 8 up rows by turns); else
+    float32.  Returns [P, N] in sorted order.
+    bfloat16: tcgen05 (tiles of 128 rows, the plan made for them), a warp a column for a handful of pairs, mma.sync
+    tiles of 64 rows between; float32, or sizes those do not take: float32 FMA."""
     _dev(a, w)
     assert a.stride(1) == 1 and w.is_contiguous() and a.dtype == w.dtype
     E, n_rows, K = w.shape
     N = n_rows // 2 if gated else n_rows
     assert a.shape[1] == K
-    out = torch.empty((plan.pairs, N), dtype=a.dtype if gated else torch.float32, device=a.device)
+    P = plan.pairs
+    out = torch.empty((P, N), dtype=a.dtype if gated else torch.float32, device=a.device)
+    bf = a.dtype == torch.bfloat16
+    if (bf and plan.row_tile == MOE_UMMA_ROW_TILE and K % 8 == 0 and (not gated or (interleaved and N % 8 == 0))
+            and w.data_ptr() % 16 == 0):
+        if gather:
+            rows = torch.empty((P, K), dtype=a.dtype, device=a.device)
+            f = _fn("moe", "fellm_moe_gather", [_c_p, _c_int, _c_p, _c_int, _c_p, _c_int, _c_int, _c_p])
+            _check(f(_p(a), a.stride(0), _p(plan.sorted), plan.top, _p(rows), P, K, _stream()), "moe_gather")
+            a = rows
+        assert a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0
+        f = _fn("gemm_umma", "fellm_gemm_umma_grouped", [_c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                                         _c_p, _c_p, _c_int, _c_p, _c_p])
+        _check(f(_p(a), _p(w), _p(out), _EPI_SWIGLU if gated else _EPI_F32, P, n_rows, K, E, a.stride(0), out.stride(0),
+                 _p(plan.table), _p(plan.n_tiles), plan.max_tiles, _p(umma_status(a.device)), _stream()), "gemm_umma_grouped")
+        return out
+    if plan.row_tile != MOE_ROW_TILE:
+        raise KernelError(f"moe_gemm: a plan of {plan.row_tile}-row tiles needs the tcgen05 grouped product (bfloat16, K % 8 == 0)")
     f = _fn("moe", "fellm_moe_gemm", [_c_p, _c_int, _c_int, _c_p, _c_int, _c_p, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int,
-                                      _c_int, _c_p, _c_p, _c_int, _c_int, _c_p])
+                                      _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_p])
     _check(f(_p(a), _is_bf16(a), a.stride(0), _p(plan.sorted) if gather else None, plan.top, _p(w), _is_bf16(w), _p(out),
-             _is_bf16(out), N, N, K, int(gated), _p(plan.table), _p(plan.n_tiles), plan.max_tiles, int(MOE_MMA), _stream()),
-           "moe_gemm")
+             _is_bf16(out), N, N, K, int(gated), _p(plan.table), _p(plan.n_tiles), plan.max_tiles, int(MOE_MMA),
+             int(interleaved), int(P <= MOE_FEW_PAIRS), _stream()), "moe_gemm")
     return out
 
 

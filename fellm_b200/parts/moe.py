@@ -6,7 +6,8 @@
     out = sum over the chosen experts, in the order of their scores, of weight * W_down (SiLU(W_gate h) * (W_up h))
 
 Experts have no biases.  Nothing goes through the host: the router's choices are sorted by expert on the device
-(ops.moe_plan) and two grouped products walk the sorted rows, the first gathering its input rows by token and
+(ops.moe_plan; the router's product and the routing are one launch, ops.moe_router) and two grouped products walk
+the sorted rows (tcgen05 for steps of many rows, mma.sync tiles between, a warp a column for a handful of tokens), the first gathering its input rows by token and
 applying SiLU(gate) * up in its epilogue, the second leaving float32 rows that ops.moe_combine adds, weighted, into
 the residual stream.  A token's result does not depend on what else is in the step.
 """
@@ -17,8 +18,7 @@ import torch
 from .. import ops
 from ..config.errors import ConfigError
 from .base import FeedForward, ParamDecl, register_part
-from .gated_delta import _pad_rows
-from .linear import linear, linear_modules
+from .linear import linear_modules
 
 
 @register_part("feed_forward", "moe")
@@ -39,19 +39,25 @@ class RoutedExperts(FeedForward):
         w = self.w
         mats = [w.pop(f"e{e}.{n}.weight") for e in range(self.E) for n in ("gate", "up", "down")]
         dt = mats[0].dtype if all(m.dtype == mats[0].dtype for m in mats) else torch.float32
-        gu = [torch.cat([mats[3 * e].to(dt), mats[3 * e + 1].to(dt)], 0) for e in range(self.E)]
-        w["gate_up.weight"] = torch.stack(gu, 0).contiguous()                                  # [E, 2 ff, d]: gate rows, then up
+        # on the tensor-core paths an expert's gate and up rows lie in blocks of 8 by turns, as the dense feed-forward's do
+        self.interleaved = dt == torch.bfloat16 and mats[0].is_cuda and self.ff % 8 == 0 and self.size % 8 == 0
+        if self.interleaved:
+            gu = [ops.interleave_gate_up(mats[3 * e], mats[3 * e + 1]) for e in range(self.E)]
+        else:
+            gu = [torch.cat([mats[3 * e].to(dt), mats[3 * e + 1].to(dt)], 0) for e in range(self.E)]
+        w["gate_up.weight"] = torch.stack(gu, 0).contiguous()                                  # [E, 2 ff, d]
         w["down.weight"] = torch.stack([mats[3 * e + 2].to(dt) for e in range(self.E)], 0).contiguous()     # [E, d, ff]
-        w["router.weight"] = _pad_rows(w["router.weight"])
+        w["router.weight"] = w["router.weight"].contiguous()
 
     def forward(self, hn, ctx, out):
         w = self.w
-        z = linear(hn, w["router.weight"], out_dtype=torch.float32)
-        idx, score = ops.moe_route(z, self.E, self.top, self.renormalize)
-        plan = ops.moe_plan(idx, self.E)
+        idx, score = ops.moe_router(hn, w["router.weight"], self.top, self.renormalize)
         if hn.dtype != w["gate_up.weight"].dtype:          # a file that stores some experts in 32-bit under a bfloat16 engine
             hn = hn.to(w["gate_up.weight"].dtype)
-        a = ops.moe_gemm(hn, w["gate_up.weight"], plan, gated=True, gather=True)
+        bf = hn.dtype == torch.bfloat16
+        tile = ops.moe_row_tile(idx.numel(), bf, self.interleaved and self.ff % 8 == 0 and self.size % 8 == 0 and hn.stride(0) % 8 == 0)
+        plan = ops.moe_plan(idx, self.E, tile)
+        a = ops.moe_gemm(hn, w["gate_up.weight"], plan, gated=True, gather=True, interleaved=self.interleaved)
         y = ops.moe_gemm(a, w["down.weight"], plan, gated=False, gather=False)
         ops.moe_combine(out, y, plan, score)
         return out
