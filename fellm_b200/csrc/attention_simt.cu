@@ -6,7 +6,7 @@
 // formulas crates/fellm-plugin-abi/src/attention_provider.rs:175-237): s_j = (q.k_j)*scale,
 // m' = max(m, s), l = l*exp(m-m') + sum exp(s-m'), acc = acc*exp(m-m') + sum p_j v_j, out = acc/l.
 //
-// One warp per (row, head).  Keys are taken in tiles of 32 that start at the first visible
+// One block per (row, head), one to eight warps.  Keys are taken in tiles of 32 that start at the first visible
 // position (0, position-window+1, or the start of the query's block of `chunk` positions), so the
 // order of every sum depends on the query's position alone: not on the cut of the prompt, the
 // batch, or the pages.
@@ -23,8 +23,22 @@
 
 #define MAX_HD 256
 
-template <typename TA, typename TC>
-__global__ void __launch_bounds__(128)
+// A block per (row, head); its `nw` warps take the row's key tiles by turns (warp w: tiles w, w + nw, ...) and their
+// partial results are added in the order of the warps.  nw is the caller's constant for a layer (from its window), never
+// the batch's or the context's: the order of every sum depends on the query's position alone.
+__device__ __forceinline__ void load8(const bf16* p, float* f) {
+  const uint4 raw = *(const uint4*)p;
+  const __nv_bfloat162* h = (const __nv_bfloat162*)&raw;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { float2 v = __bfloat1622float2(h[e]); f[2 * e] = v.x; f[2 * e + 1] = v.y; }
+}
+__device__ __forceinline__ void load8(const float* p, float* f) {
+  *(float4*)f = *(const float4*)p;
+  *(float4*)(f + 4) = *(const float4*)(p + 4);
+}
+
+template <typename TA, typename TC, bool VEC>
+__global__ void __launch_bounds__(256)
 paged_attention_simt_kernel(const TA* __restrict__ q, const TC* __restrict__ pool,
                             const int* __restrict__ block_table, int max_pages,
                             const int* __restrict__ positions, const int* __restrict__ row_slot,
@@ -33,21 +47,19 @@ paged_attention_simt_kernel(const TA* __restrict__ q, const TC* __restrict__ poo
                             const float* __restrict__ gate, int ldg, const float* __restrict__ slopes,
                             float qt_coef, int qt_every) {
   FELLM_TRACE_SCOPE(TRACE_ATTENTION_SIMT);
-  extern __shared__ float qs_all[];                 // [warps per block][hd]
-  int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int warp = blockIdx.x * (blockDim.x >> 5) + wib;
-  if (warp >= T * H) return;
-  int row = warp / H, h = warp - row * H;
-  int g = h / (H / G);
-  float* qs = qs_all + (size_t)wib * hd;
+  extern __shared__ __align__(16) float qs[];       // [hd rounded up to 8] the query; then [nw][vd + 2] the warps' parts
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int row = blockIdx.x / H, h = blockIdx.x - row * H;
+  const int g = h / (H / G);
   const TA* qr = q + (size_t)row * ldq + (size_t)h * hd;
   int pos = positions[row];
   const float qt = qt_every > 0 ? 1.0f + qt_coef * logf((float)((pos + 1) / qt_every + 1)) : 1.0f;
-  for (int e = lane; e < hd; e += 32) qs[e] = to_f(qr[e]) * qt;
-  __syncwarp();
+  for (int e = threadIdx.x; e < hd; e += blockDim.x) qs[e] = to_f(qr[e]) * qt;
+  __syncthreads();
   const float slope = slopes ? slopes[h] : 0.f;
   const bool v_is_k = vd == 0;          // the values are the keys: nothing else is stored
   if (v_is_k) vd = hd;
+  float* parts = qs + ((hd + 7) & ~7);
   const int* bt = block_table + (size_t)row_slot[row] * max_pages;
   int k_begin = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
   if (chunk > 0) k_begin = max(k_begin, (pos / chunk) * chunk);
@@ -58,7 +70,7 @@ paged_attention_simt_kernel(const TA* __restrict__ q, const TC* __restrict__ poo
 #pragma unroll
   for (int i = 0; i < MAX_HD / 32; ++i) acc[i] = 0.f;
 
-  for (int k0 = k_begin; k0 <= pos; k0 += 32) {
+  for (int k0 = k_begin + 32 * w; k0 <= pos; k0 += 32 * nw) {
     int kj = k0 + lane;
     float s = -INFINITY;
     const TC* vrow = nullptr;
@@ -69,7 +81,16 @@ paged_attention_simt_kernel(const TA* __restrict__ q, const TC* __restrict__ poo
       const TC* krow = rec + tok * hd;
       vrow = v_is_k ? krow : rec + (size_t)G * page_tokens * hd + tok * vd;
       float dot = 0.f;
-      for (int e = 0; e < hd; ++e) dot = fmaf(qs[e], to_f(krow[e]), dot);
+      if (VEC) {
+        for (int e0 = 0; e0 < hd; e0 += 8) {
+          float kf[8];
+          load8(krow + e0, kf);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) dot = fmaf(qs[e0 + e], kf[e], dot);
+        }
+      } else {
+        for (int e = 0; e < hd; ++e) dot = fmaf(qs[e], to_f(krow[e]), dot);
+      }
       s = dot * scale;
       if (softcap > 0.f) s = softcap * tanhf(s / softcap);
       s -= slope * (float)(pos - kj);
@@ -90,6 +111,27 @@ paged_attention_simt_kernel(const TA* __restrict__ q, const TC* __restrict__ poo
         int e = lane + 32 * i;
         if (e < vd) acc[i] = fmaf(pj, to_f(vj[e]), acc[i]);
       }
+    }
+  }
+  if (nw > 1) {
+    // the warps' parts, added in the order of the warps (a warp without a tile holds m = -inf, l = 0)
+    float* mine = parts + (size_t)w * (vd + 2);
+#pragma unroll
+    for (int i = 0; i < MAX_HD / 32; ++i) { int e = lane + 32 * i; if (e < vd) mine[e] = acc[i]; }
+    if (lane == 0) { mine[vd] = m; mine[vd + 1] = l; }
+    __syncthreads();
+    if (w != 0) return;
+    float M = -INFINITY;
+    for (int u = 0; u < nw; ++u) M = fmaxf(M, parts[(size_t)u * (vd + 2) + vd]);
+    l = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_HD / 32; ++i) acc[i] = 0.f;
+    for (int u = 0; u < nw; ++u) {
+      const float* pu = parts + (size_t)u * (vd + 2);
+      const float f = expf(pu[vd] - M);
+      l = fmaf(pu[vd + 1], f, l);
+#pragma unroll
+      for (int i = 0; i < MAX_HD / 32; ++i) { int e = lane + 32 * i; if (e < vd) acc[i] = fmaf(pu[e], f, acc[i]); }
     }
   }
   TA* o = out + ((size_t)row * H + h) * vd;
@@ -153,25 +195,24 @@ FELLM_API int fellm_paged_attention_general(const void* q, int act_bf16, const v
                                             const int* row_slot, void* out, int T, int H, int G, int hd,
                                             int page_tokens, int layer, int layers_in_group, float scale,
                                             int window, int vd, int ldq, float softcap, int chunk, const float* gate,
-                                            int ldg, const float* slopes, float qt_coef, int qt_every,
+                                            int ldg, const float* slopes, float qt_coef, int qt_every, int warps,
                                             cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (hd < 1 || hd > MAX_HD || vd < 0 || vd > MAX_HD) return FELLM_ERR_SIZE;
+  if (hd < 1 || hd > MAX_HD || vd < 0 || vd > MAX_HD || warps < 1 || warps > 8) return FELLM_ERR_SIZE;
   if (G < 1 || H % G) return FELLM_ERR_SIZE;
   if (!q || !pool || !block_table || !positions || !row_slot || !out) return FELLM_ERR_ARG;
   if (act_bf16 != cache_bf16) return FELLM_ERR_ARG;
-  int warps_per_block = 4;
-  long long warps = (long long)T * H;
-  unsigned blocks = (unsigned)((warps + warps_per_block - 1) / warps_per_block);
-  size_t smem = (size_t)warps_per_block * hd * sizeof(float);
-  if (act_bf16)
-    paged_attention_simt_kernel<bf16, bf16><<<blocks, warps_per_block * 32, smem, stream>>>((const bf16*)q,
-        (const bf16*)pool, block_table, max_pages, positions, row_slot, (bf16*)out, T, H, G, hd, page_tokens,
-        layer, layers_in_group, scale, window, vd, ldq, softcap, chunk, gate, ldg, slopes, qt_coef, qt_every);
-  else
-    paged_attention_simt_kernel<float, float><<<blocks, warps_per_block * 32, smem, stream>>>((const float*)q,
-        (const float*)pool, block_table, max_pages, positions, row_slot, (float*)out, T, H, G, hd, page_tokens,
-        layer, layers_in_group, scale, window, vd, ldq, softcap, chunk, gate, ldg, slopes, qt_coef, qt_every);
+  const int out_d = vd ? vd : hd;
+  const size_t smem = ((size_t)((hd + 7) & ~7) + (size_t)warps * (out_d + 2)) * sizeof(float);
+  const unsigned blocks = (unsigned)((long long)T * H);
+  // 16 bytes of a key at a time where every key row starts on such a boundary
+  const bool vec = hd % 8 == 0 && ((uintptr_t)pool % 16) == 0 && (vd == 0 || vd % 8 == 0);
+#define PA(TA_, VEC_) paged_attention_simt_kernel<TA_, TA_, VEC_><<<blocks, warps * 32, smem, stream>>>((const TA_*)q, \
+        (const TA_*)pool, block_table, max_pages, positions, row_slot, (TA_*)out, T, H, G, hd, page_tokens, \
+        layer, layers_in_group, scale, window, vd, ldq, softcap, chunk, gate, ldg, slopes, qt_coef, qt_every)
+  if (act_bf16) { if (vec) PA(bf16, true); else PA(bf16, false); }
+  else { if (vec) PA(float, true); else PA(float, false); }
+#undef PA
   return launch_status();
 }
 
@@ -182,5 +223,5 @@ FELLM_API int fellm_paged_attention_simt(const void* q, int act_bf16, const void
                                          int window, cudaStream_t stream) {
   return fellm_paged_attention_general(q, act_bf16, pool, cache_bf16, block_table, max_pages, positions, row_slot, out,
                                        T, H, G, hd, page_tokens, layer, layers_in_group, scale, window, hd, H * hd, 0.f,
-                                       0, nullptr, 0, nullptr, 0.f, 0, stream);
+                                       0, nullptr, 0, nullptr, 0.f, 0, 1, stream);
 }

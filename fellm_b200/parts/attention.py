@@ -71,6 +71,10 @@ class Attention(Mixer):
         if self.values_are_keys and self.vd != self.hd:
             raise ConfigError(f"attention: values that are the keys have the keys' size {self.hd}, not {self.vd}")
         self.general = general
+        # warps that share a (row, head)'s keys in the CUDA-core kernel: by the window (or chunk) alone, so that the order
+        # of a row's sums is the same in every step
+        span = min(x for x in (self.window, None if chunk is None else int(chunk), 1 << 30) if x)
+        self.simt_warps = max(1, min(8, -(-span // 128)))
         if self.general:
             if self.qk_norm or self.position.inv_freq is not None or self.shares_cache:
                 raise ConfigError("attention: a soft cap, v_dim, chunk or head gate goes with no QK norm, no rotation "
@@ -178,7 +182,7 @@ class Attention(Mixer):
             a = ops.paged_attention_general(qkv, H, hd, vd, cache.pool, cache.block_table, ctx.positions, ctx.row_slot,
                                             cache.layer, cache.page_tokens, G, self.scale, window=self.window,
                                             chunk=self.chunk, softcap=self.softcap, gate=gate,
-                                            slopes=self.w.get("slopes"), q_temp=self.q_temp)
+                                            slopes=self.w.get("slopes"), q_temp=self.q_temp, warps=self.simt_warps)
         linear(a, self.w["out_proj.weight"], self.w.get("out_proj.bias"), out=out, accumulate=True)
         return out
 

@@ -76,7 +76,7 @@ def test_attention_at_the_edges_of_windows_and_pages(dtype, window, page, hd):
     seen: the key just outside the window must not count and the oldest inside must; the slopes and the query
     temperature (a step every 3 positions) move the winner.  The values are the keys: the cache holds keys alone.
     Rows come as two requests whose pages interleave, in portions that end before, on and behind the edges, single
-    rows among them."""
+    rows among them; one to four warps share a row's keys."""
     from fellm_b200 import ops
     H, G, T = 4, 2, 2 * max(window, page) + 7
     T = min(T, 150)
@@ -102,7 +102,7 @@ def test_attention_at_the_edges_of_windows_and_pages(dtype, window, page, hd):
             pos, slot = _i32(list(range(at, at + n))), _i32([r] * n)
             ops.kv_write(qk[at:at + n], k_off, k_off, pool, table, pos, slot, 0, page, G, hd, 0)
             got.append(ops.paged_attention_general(qk[at:at + n], H, hd, 0, pool, table, pos, slot, 0, page, G, 0.6,
-                                                   window=window, slopes=slopes, q_temp=(0.8, 3)))
+                                                   window=window, slopes=slopes, q_temp=(0.8, 3), warps=1 + window % 4))
             at += n
         got = torch.cat(got).double().cpu()
         tol = 1e-4 if dtype == torch.float32 else 2e-2
