@@ -37,7 +37,8 @@ __device__ __forceinline__ void load8(const float* p, float* f) {
   *(float4*)(f + 4) = *(const float4*)(p + 4);
 }
 
-template <typename TA, typename TC, bool VEC>
+// NACC: registers a lane keeps of the read-out (elements lane, lane + 32, ...): the value size over 32, rounded up.
+template <typename TA, typename TC, bool VEC, int NACC>
 __global__ void __launch_bounds__(256)
 paged_attention_simt_kernel(const TA* __restrict__ q, const TC* __restrict__ pool,
                             const int* __restrict__ block_table, int max_pages,
@@ -66,9 +67,9 @@ paged_attention_simt_kernel(const TA* __restrict__ q, const TC* __restrict__ poo
   const size_t record = (size_t)G * page_tokens * (v_is_k ? hd : hd + vd);       // one page of one layer: keys, then values
 
   float m = -INFINITY, l = 0.f;
-  float acc[MAX_HD / 32];
+  float acc[NACC];
 #pragma unroll
-  for (int i = 0; i < MAX_HD / 32; ++i) acc[i] = 0.f;
+  for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
 
   for (int k0 = k_begin + 32 * w; k0 <= pos; k0 += 32 * nw) {
     int kj = k0 + lane;
@@ -101,13 +102,14 @@ paged_attention_simt_kernel(const TA* __restrict__ q, const TC* __restrict__ poo
     l = l * corr + warp_sum(p);
     m = m_new;
 #pragma unroll
-    for (int i = 0; i < MAX_HD / 32; ++i) acc[i] *= corr;
+    for (int i = 0; i < NACC; ++i) acc[i] *= corr;
     int n_valid = pos - k0 + 1 < 32 ? pos - k0 + 1 : 32;
+#pragma unroll 4
     for (int j = 0; j < n_valid; ++j) {
       float pj = __shfl_sync(0xffffffffu, p, j);
       const TC* vj = (const TC*)__shfl_sync(0xffffffffu, (unsigned long long)vrow, j);
 #pragma unroll
-      for (int i = 0; i < MAX_HD / 32; ++i) {
+      for (int i = 0; i < NACC; ++i) {
         int e = lane + 32 * i;
         if (e < vd) acc[i] = fmaf(pj, to_f(vj[e]), acc[i]);
       }
@@ -117,7 +119,7 @@ paged_attention_simt_kernel(const TA* __restrict__ q, const TC* __restrict__ poo
     // the warps' parts, added in the order of the warps (a warp without a tile holds m = -inf, l = 0)
     float* mine = parts + (size_t)w * (vd + 2);
 #pragma unroll
-    for (int i = 0; i < MAX_HD / 32; ++i) { int e = lane + 32 * i; if (e < vd) mine[e] = acc[i]; }
+    for (int i = 0; i < NACC; ++i) { int e = lane + 32 * i; if (e < vd) mine[e] = acc[i]; }
     if (lane == 0) { mine[vd] = m; mine[vd + 1] = l; }
     __syncthreads();
     if (w != 0) return;
@@ -125,20 +127,20 @@ paged_attention_simt_kernel(const TA* __restrict__ q, const TC* __restrict__ poo
     for (int u = 0; u < nw; ++u) M = fmaxf(M, parts[(size_t)u * (vd + 2) + vd]);
     l = 0.f;
 #pragma unroll
-    for (int i = 0; i < MAX_HD / 32; ++i) acc[i] = 0.f;
+    for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
     for (int u = 0; u < nw; ++u) {
       const float* pu = parts + (size_t)u * (vd + 2);
       const float f = expf(pu[vd] - M);
       l = fmaf(pu[vd + 1], f, l);
 #pragma unroll
-      for (int i = 0; i < MAX_HD / 32; ++i) { int e = lane + 32 * i; if (e < vd) acc[i] = fmaf(pu[e], f, acc[i]); }
+      for (int i = 0; i < NACC; ++i) { int e = lane + 32 * i; if (e < vd) acc[i] = fmaf(pu[e], f, acc[i]); }
     }
   }
   TA* o = out + ((size_t)row * H + h) * vd;
   float inv_l = 1.0f / l;
   if (gate) inv_l *= 1.0f / (1.0f + expf(-gate[(size_t)row * ldg + h]));
 #pragma unroll
-  for (int i = 0; i < MAX_HD / 32; ++i) {
+  for (int i = 0; i < NACC; ++i) {
     int e = lane + 32 * i;
     if (e < vd) o[e] = from_f<TA>(acc[i] * inv_l);
   }
@@ -207,11 +209,14 @@ FELLM_API int fellm_paged_attention_general(const void* q, int act_bf16, const v
   const unsigned blocks = (unsigned)((long long)T * H);
   // 16 bytes of a key at a time where every key row starts on such a boundary
   const bool vec = hd % 8 == 0 && ((uintptr_t)pool % 16) == 0 && (vd == 0 || vd % 8 == 0);
-#define PA(TA_, VEC_) paged_attention_simt_kernel<TA_, TA_, VEC_><<<blocks, warps * 32, smem, stream>>>((const TA_*)q, \
+#define PA(TA_, VEC_, NACC_) paged_attention_simt_kernel<TA_, TA_, VEC_, NACC_><<<blocks, warps * 32, smem, stream>>>((const TA_*)q, \
         (const TA_*)pool, block_table, max_pages, positions, row_slot, (TA_*)out, T, H, G, hd, page_tokens, \
         layer, layers_in_group, scale, window, vd, ldq, softcap, chunk, gate, ldg, slopes, qt_coef, qt_every)
-  if (act_bf16) { if (vec) PA(bf16, true); else PA(bf16, false); }
-  else { if (vec) PA(float, true); else PA(float, false); }
+#define PA_N(TA_, VEC_) do { if (out_d <= 32) PA(TA_, VEC_, 1); else if (out_d <= 64) PA(TA_, VEC_, 2); \
+                             else if (out_d <= 128) PA(TA_, VEC_, 4); else PA(TA_, VEC_, 8); } while (0)
+  if (act_bf16) { if (vec) PA_N(bf16, true); else PA_N(bf16, false); }
+  else { if (vec) PA_N(float, true); else PA_N(float, false); }
+#undef PA_N
 #undef PA
   return launch_status();
 }

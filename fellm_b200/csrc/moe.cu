@@ -419,6 +419,7 @@ __device__ __forceinline__ void unpack8(const uint4& raw, float* f) {
 #pragma unroll
   for (int e = 0; e < 4; ++e) { float2 v = __bfloat1622float2(h[e]); f[2 * e] = v.x; f[2 * e + 1] = v.y; }
 }
+// A warp's columns: n and, GATED, its up partner; not gated: n and n + 1 (two weight rows against the same rows of A).
 template <typename TO, bool GATED>
 __global__ void __launch_bounds__(VW * 32)
 moe_gemv_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__ gather, int top,
@@ -427,11 +428,12 @@ moe_gemv_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__ gat
   if ((int)blockIdx.x >= *n_tiles) return;
   const int e = table[3 * blockIdx.x], row0 = table[3 * blockIdx.x + 1], rows = table[3 * blockIdx.x + 2];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n = blockIdx.y * VW + warp;
+  const int n = GATED ? blockIdx.y * VW + warp : 2 * (blockIdx.y * VW + warp);
   if (n >= N) return;
+  const bool two = !GATED && n + 1 < N;
   const bf16* We = W + (size_t)e * (GATED ? 2 : 1) * N * K;
-  const bf16* wg = We + (size_t)(GATED ? gate_row(n, inter) : n) * K;
-  const bf16* wu = GATED ? We + (size_t)up_row(n, N, inter) * K : nullptr;
+  const bf16* w0 = We + (size_t)(GATED ? gate_row(n, inter) : n) * K;
+  const bf16* w1 = GATED ? We + (size_t)up_row(n, N, inter) * K : (two ? w0 + K : w0);
   for (int r0 = 0; r0 < rows; r0 += VR) {
     const bf16* ar[VR];
 #pragma unroll
@@ -439,32 +441,45 @@ moe_gemv_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__ gat
       const int r = min(r0 + i, rows - 1);
       ar[i] = A + (size_t)(gather ? gather[row0 + r] / top : row0 + r) * lda;
     }
-    float sg[VR], su[VR];
+    const int nr = min(VR, rows - r0);
+    float s0[VR], s1[VR];
 #pragma unroll
-    for (int i = 0; i < VR; ++i) sg[i] = su[i] = 0.f;
-    for (int k = lane * 8; k < K; k += 256) {
-      float fg[8], fu[8];
-      unpack8(*(const uint4*)(wg + k), fg);
-      if (GATED) unpack8(*(const uint4*)(wu + k), fu);
+    for (int i = 0; i < VR; ++i) s0[i] = s1[i] = 0.f;
+    // two steps of K at once: four 16-byte loads of weights in flight a lane before the first is used
+    for (int k = lane * 8; k < K; k += 512) {
+      const bool second = k + 256 < K;
+      const uint4 zero = make_uint4(0, 0, 0, 0);
+      const uint4 ra0 = *(const uint4*)(w0 + k), rb0 = *(const uint4*)(w1 + k);
+      const uint4 ra1 = second ? *(const uint4*)(w0 + k + 256) : zero, rb1 = second ? *(const uint4*)(w1 + k + 256) : zero;
+      uint4 xa[VR], xb[VR];
 #pragma unroll
       for (int i = 0; i < VR; ++i) {
-        float fa[8];
-        unpack8(*(const uint4*)(ar[i] + k), fa);
+        xa[i] = i < nr ? *(const uint4*)(ar[i] + k) : zero;
+        xb[i] = (i < nr && second) ? *(const uint4*)(ar[i] + k + 256) : zero;
+      }
+      float f0[8], f1[8], g0[8], g1[8];
+      unpack8(ra0, f0); unpack8(rb0, f1); unpack8(ra1, g0); unpack8(rb1, g1);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) { sg[i] = fmaf(fa[j], fg[j], sg[i]); if (GATED) su[i] = fmaf(fa[j], fu[j], su[i]); }
+      for (int i = 0; i < VR; ++i) {
+        float fa[8], fb[8];
+        unpack8(xa[i], fa); unpack8(xb[i], fb);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { s0[i] = fmaf(fa[j], f0[j], s0[i]); s1[i] = fmaf(fa[j], f1[j], s1[i]); }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { s0[i] = fmaf(fb[j], g0[j], s0[i]); s1[i] = fmaf(fb[j], g1[j], s1[i]); }
       }
     }
 #pragma unroll
     for (int i = 0; i < VR; ++i) {
-      float g = warp_sum(sg[i]);
-      float u = GATED ? warp_sum(su[i]) : 0.f;
+      float a = warp_sum(s0[i]), b = warp_sum(s1[i]);
       if (lane == 0 && r0 + i < rows) {
-        float v = g;
         if (GATED) {
-          g = to_f(from_f<bf16>(g)); u = to_f(from_f<bf16>(u));
-          v = g / (1.0f + expf(-g)) * u;
+          a = to_f(from_f<bf16>(a)); b = to_f(from_f<bf16>(b));
+          C[(size_t)(row0 + r0 + i) * ldc + n] = from_f<TO>(a / (1.0f + expf(-a)) * b);
+        } else {
+          C[(size_t)(row0 + r0 + i) * ldc + n] = from_f<TO>(a);
+          if (two) C[(size_t)(row0 + r0 + i) * ldc + n + 1] = from_f<TO>(b);
         }
-        C[(size_t)(row0 + r0 + i) * ldc + n] = from_f<TO>(v);
       }
     }
   }
@@ -481,7 +496,7 @@ FELLM_API int fellm_moe_gemm(const void* A, int a_bf16, int lda, const int* gath
   if (a_bf16 != w_bf16 || (!gated && c_bf16) || (gated && c_bf16 != a_bf16)) return FELLM_ERR_ARG;
   const bool mma = use_mma && a_bf16 && K % 8 == 0 && lda % 8 == 0 && ((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0;
   if (mma && few_rows) {
-    dim3 grid(max_tiles, (N + VW - 1) / VW);
+    dim3 grid(max_tiles, gated ? (N + VW - 1) / VW : (N + 2 * VW - 1) / (2 * VW));
     if (gated)
       moe_gemv_kernel<bf16, true><<<grid, VW * 32, 0, stream>>>((const bf16*)A, lda, gather, top, (const bf16*)W, (bf16*)C, ldc, N, K, table, n_tiles, inter);
     else
