@@ -338,7 +338,7 @@ def samusun_config(width, ff, layers, vocab):
     turns dense (`ff`) and routed (8 experts of ff / 2, two a token: the same work a token, four times the weights);
     every layer is mixer and feed-forward side by side behind one norm; no loop."""
     H = width // 64
-    att = dict(dim=64, heads=H, kv_heads=max(H // 4, 1), mask=dict(size=1024), q_temp=dict(coef=0.3, every=256),
+    att = dict(dim=64, heads=H, kv_heads=max(H // 4, 1), mask=dict(size=1024), q_temp=dict(coef=0.25, every=128),
                scale=0.125, vdim=64)
     R = max(width // 128, 1)
     ret = dict(decay=[1.0 - 2.0 ** -(5 + 3 * h / R) for h in range(R)], dim=128, heads=R, rot=dict(base=10000.0, dims=64), vdim=128)

@@ -81,7 +81,7 @@ CFG_D = config(101, 72, [
 # W: not tiny: the sizes at which the products run on their tensor-core kernels, the attention of portions on its
 # own and the experts' grouped products on theirs
 CFG_W = config(256, 1024, [
-    layer("attention", attention(16, 4, 64, 100, 0.125, 0.3, 32), dense(2048)),
+    layer("attention", attention(16, 4, 64, 100, 0.125, 0.35, 32), dense(2048)),
     layer("retention", retention(8, 128, 64, [1 - 2.0 ** -(3 + i) for i in range(8)], 64, 10000.0), moe(512, 8, 2)),
 ], emb=1.0, logit_scale=1.0)
 
@@ -160,3 +160,43 @@ def run_cuts(engine, req, toks, cuts):
     engine.check_status()
     engine.release(req)
     return torch.cat(out)
+
+
+def random_config(seed: int):
+    """A configuration drawn at random: 2 to 5 layers of either kind in any order, heads and sizes that are and are
+    not multiples of anything, windows from 1 to beyond the prompt, any feed-forward or none, a loop or none."""
+    rng = np.random.default_rng(7000 + seed)
+    pick = lambda xs: xs[int(rng.integers(0, len(xs)))]
+    width = int(pick([48, 64, 72, 96, 128, 136]))
+    n_layers = int(rng.integers(2, 6))
+    layers = []
+    for _ in range(n_layers):
+        if rng.random() < 0.55:
+            G = int(pick([1, 2, 3]))
+            H = G * int(pick([1, 2, 4]))
+            m = attention(H, G, int(pick([4, 8, 12, 16, 24, 32, 40, 48, 64])), int(pick([1, 2, 5, 15, 16, 17, 31, 40, 64, 100, 1000])),
+                          float(rng.uniform(0.1, 0.5)), float(rng.uniform(0.0, 1.0)), int(pick([1, 2, 3, 7, 16, 50])))
+            kind = "attention"
+        else:
+            H = int(pick([1, 2, 3, 5]))
+            dk = int(pick([4, 8, 12, 16, 24, 32, 64, 96]))
+            rot = int(pick([0, 2, dk // 2 - (dk // 2) % 2, dk]))
+            m = retention(H, dk, int(pick([4, 8, 12, 20, 32, 64, 80])), [float(1.0 - 2.0 ** -rng.uniform(1, 9)) for _ in range(H)],
+                          rot, float(pick([10.0, 10000.0, 1e6])))
+            kind = "retention"
+        r = rng.random()
+        if r < 0.25:
+            mlp = None
+        elif r < 0.6:
+            mlp = dense(int(pick([8, 24, 40, 64, 100, 160])))
+        else:
+            E = int(pick([1, 2, 3, 4, 6, 8, 12]))
+            mlp = moe(int(pick([8, 9, 16, 24, 40, 64])), E, int(rng.integers(1, E + 1)))
+        layers.append(layer(kind, m, mlp))
+    loop = None
+    if rng.random() < 0.6:
+        a = int(rng.integers(0, n_layers))
+        b = int(rng.integers(a + 1, n_layers + 1))
+        loop = (a, b, int(rng.integers(1, 4)))
+    return config(int(pick([50, 101, 128, 200, 333])), width, layers, loop=loop, eps=float(pick([1e-5, 1e-6])),
+                  emb=float(rng.uniform(0.3, 2.0)), logit_scale=float(rng.uniform(0.3, 2.0)), cap=float(rng.uniform(5.0, 40.0)))

@@ -471,6 +471,48 @@ def test_scaled_queries_and_keys_show_a_wrong_window(engines):
         assert U.distance(got, want) < 5 * U.LIMIT[engines.dtype], window
 
 
+@pytest.mark.parametrize("seed", range(10))
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_configurations_drawn_at_random(seed, dtype):
+    """Ten models of random shape, each under three regimes: the whole prompt, portions down to two tokens followed by
+    single tokens, and two unequal requests sharing every step."""
+    from fellm_b200.engine import StepItem
+    from fellm_b200.weights import write_model_folder
+    cfg = U.random_config(seed)
+    folder = str(write_model_folder(Path(U._tmp.name) / f"random_{seed}", cfg, 500 + seed))
+    _, w = U.load_folder(folder)
+    eng = U.make_engine(folder, dtype, max_tokens=512)
+    rng = np.random.default_rng(seed)
+    T = 75
+    toks = [int(t) for t in rng.integers(0, cfg["vocab"], T)]
+    other = [int(t) for t in rng.integers(0, cfg["vocab"], 41)]
+    want, want_other = P.forward(toks, w, cfg), P.forward(other, w, cfg)
+    limit = U.LIMIT[dtype] * (3 if dtype == "bfloat16" else 1)      # (several passes of a loop add up their rounding)
+    assert U.distance(U.run_cuts(eng, "whole", toks, [T]), want) < limit, cfg
+    assert U.distance(U.run_cuts(eng, "cut", toks, [2, 17, 2, 3, 31]), want) < limit, cfg
+    eng.add_request("a")
+    eng.add_request("b")
+    got_a, got_b, at_a, at_b = [], [], 0, 0
+    sizes_a, sizes_b = [5, 1, 30, 2], [1, 1, 16, 7, 2]
+    while at_a < T or at_b < len(other):
+        items = []
+        na = min(sizes_a.pop(0) if sizes_a else 1, T - at_a)
+        nb = min(sizes_b.pop(0) if sizes_b else 1, len(other) - at_b)
+        if na > 0:
+            items.append(StepItem("a", toks[at_a:at_a + na], list(range(na))))
+        if nb > 0:
+            items.append(StepItem("b", other[at_b:at_b + nb], list(range(nb))))
+        lg = eng.step(items)
+        if na > 0:
+            got_a.append(lg[:na].clone())
+        if nb > 0:
+            got_b.append(lg[max(na, 0):max(na, 0) + nb].clone())
+        at_a, at_b = at_a + max(na, 0), at_b + max(nb, 0)
+    eng.check_status()
+    assert U.distance(torch.cat(got_a), want) < limit, cfg
+    assert U.distance(torch.cat(got_b), want_other) < limit, cfg
+
+
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_greedy_generation_through_the_scheduler(name):
     """Engine.generate_batch (scheduler, sampler, CUDA graphs on) in float32 against the plain implementation's greedy
