@@ -479,6 +479,36 @@ def retention_scan(qkv, k_off, v_off, positions, inv_freq, rot_dim, decay, kscal
     return out
 
 
+RETENTION_CHUNKED = os.environ.get("FELLM_B200_RETENTION_CHUNKED", "1") != "0"
+RETENTION_CHUNK_MIN_ROWS = int(os.environ.get("FELLM_B200_RETENTION_CHUNK_MIN_ROWS", 128))     # shorter portions: the scan (0.25 us a token)
+
+
+def retention_chunked(p, k_off, v_off, positions, inv_freq, rot_dim, decay, kscale, state, item_start, item_slot, n_items,
+                      max_item_rows, H, dk, dv, out=None):
+    """Retention over portions in blocks of 64 tokens (float32 arithmetic; the blocks of a prompt run side by side and
+    only the states in front of the blocks are walked in order).  Arguments as retention_scan's, p float32; the sums run
+    in another order than the scan's (equal up to float32 rounding)."""
+    _dev(p, positions, inv_freq, decay, state, item_start, item_slot)
+    T = p.shape[0]
+    assert p.dtype == torch.float32 and p.stride(1) == 1 and decay.dtype == torch.float32 and decay.numel() == H
+    assert rot_dim % 2 == 0 and 0 <= rot_dim <= dk
+    if rot_dim:
+        assert inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dim // 2 and inv_freq.is_contiguous()
+    _i32(positions, "positions"), _i32(item_start, "item_start"), _i32(item_slot, "item_slot")
+    if out is None:
+        out = torch.empty((T, H * dv), dtype=torch.float32, device=p.device)
+    blocks = -(-max_item_rows // 64)
+    scratch = torch.empty(2 * T * H * dk + n_items * blocks * H * dk * dv, dtype=torch.float32, device=p.device)
+    st, stride = _state_args(state)
+    f = _fn("retention_chunk", "fellm_retention_chunked",
+            [_c_p, _c_int, _c_int, _c_int, _c_p, _c_p, _c_int, _c_p, _c_f, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int,
+             _c_int, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_p(p), p.stride(0), k_off, v_off, _p(positions), _p(inv_freq) if rot_dim else None, rot_dim, _p(decay),
+             float(kscale), st, stride, _p(item_start), _p(item_slot), _p(out), _p(scratch), T, n_items, int(max_item_rows),
+             H, dk, dv, _stream()), "retention_chunked")
+    return out
+
+
 _GATE_ACT = {None: 0, "silu": 1, "sigmoid": 2}
 
 

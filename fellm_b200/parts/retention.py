@@ -9,6 +9,8 @@
 Kept per request, float32: S [H, dk, dv], zero when the request starts.  Float32 in both engines: the angles and the
 rotation, the scaling of k, the decay, the state and its read-out, the unit norm.  The four projections are one
 product whose result is stored in float32, so that nothing that enters the recurrence is rounded to bfloat16 again.
+Token by token the recurrence is the engine's scan (csrc/recurrent.cu); prompt portions of the bfloat16 engine run in
+blocks of 64 tokens side by side (csrc/retention_chunk.cu).
 """
 from __future__ import annotations
 
@@ -65,9 +67,16 @@ class Retention(Mixer):
             raise ConfigError("a retention layer cannot run on another layer's state")
         w, off, H, dk, dv = self.w, self.off, self.H, self.dk, self.dv
         p = linear(xn, w["in.weight"], out_dtype=torch.float32)             # [T, q | k | v | g] float32
-        o = ops.retention_scan(p, off["k"], off["v"], ctx.positions, self.position.inv_freq, self.rot_dim, w["decay"],
-                               self.key_scale, cache.states, ctx.item_start, cache.item_slot, ctx.n_items, H, dk, dv,
-                               max_item_rows=ctx.max_item_rows)
+        if xn.dtype == torch.bfloat16 and ops.RETENTION_CHUNKED and ctx.max_item_rows >= ops.RETENTION_CHUNK_MIN_ROWS:
+            # portions of prompts in the bfloat16 engine: blocks of 64 tokens side by side (float32 arithmetic, another
+            # order of the sums than the scan's; the 32-bit engine keeps the scan and the same bits under every cut)
+            o = ops.retention_chunked(p, off["k"], off["v"], ctx.positions, self.position.inv_freq, self.rot_dim, w["decay"],
+                                      self.key_scale, cache.states, ctx.item_start, cache.item_slot, ctx.n_items,
+                                      ctx.max_item_rows, H, dk, dv)
+        else:
+            o = ops.retention_scan(p, off["k"], off["v"], ctx.positions, self.position.inv_freq, self.rot_dim, w["decay"],
+                                   self.key_scale, cache.states, ctx.item_start, cache.item_slot, ctx.n_items, H, dk, dv,
+                                   max_item_rows=ctx.max_item_rows)
         y = ops.head_norm_gate(o, None, False, p[:, off["g"]:off["g"] + H * dv], "silu", self.eps, H, dv, xn.dtype)
         linear(y, w["o.weight"], out=out, accumulate=True)
         return out
@@ -76,4 +85,4 @@ class Retention(Mixer):
         return [self.w["in.weight"], self.w["o.weight"]]
 
     def kernel_modules(self, dtype):
-        return linear_modules(dtype) + [("recurrent", None)]
+        return linear_modules(dtype) + [("recurrent", None)] + ([("retention_chunk", None)] if dtype == "bfloat16" else [])

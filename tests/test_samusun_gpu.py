@@ -192,6 +192,46 @@ def test_retention_scan(H, dk, dv, rot, dtype):
     assert float(state[0].min()) == 9.0 and float(state[2].max()) == 9.0       # the neighbours' slots are untouched
 
 
+@pytest.mark.parametrize("H,dk,dv,rot", [(3, 20, 12, 8), (2, 32, 48, 32), (1, 64, 64, 16), (2, 128, 128, 64), (1, 200, 5, 6), (2, 8, 150, 0)])
+def test_retention_in_blocks_of_tokens(H, dk, dv, rot):
+    """The blocked form against the plain recurrence and against the scan: two requests in one launch with portions of
+    unequal length (1, 2, 63, 64, 65 and 200 tokens among them: inside a block, on its edge, over several blocks), each
+    going on from the state and the position its last portion left; the states end equal to the scan's."""
+    from fellm_b200 import ops
+    T = [330, 333]
+    g = torch.Generator().manual_seed(H * 10 + dk)
+    decay = [1.0 - 0.5 ** (2 + 3 * h) for h in range(H)]
+    base = 300.0
+    inv_freq = torch.tensor([base ** (-2.0 * i / rot) for i in range(rot // 2)], dtype=torch.float64).float().to(DEV) if rot else None
+    dec = torch.tensor(decay, dtype=torch.float32, device=DEV)
+    k_off, v_off = H * dk, 2 * H * dk + 4
+    rows, wants = [], []
+    for r in range(2):
+        q, k, v = (torch.randn(T[r], H, d_, generator=g) for d_ in (dk, dk, dv))
+        wants.append(_retention_want(q, k, v, decay, rot, base, dk).reshape(T[r], H * dv))
+        rows.append(torch.cat([q.reshape(T[r], -1), k.reshape(T[r], -1), torch.zeros(T[r], 4), v.reshape(T[r], -1)], 1).to(DEV))
+    state = torch.full((4, H, dk, dv), 7.0, device=DEV)
+    state[1].zero_()
+    state[3].zero_()
+    scan_state = state.clone()
+    cuts = [[64, 1, 200, 65], [2, 63, 130, 138]]
+    at = [0, 0]
+    for step in range(4):
+        n = [cuts[0][step], cuts[1][step]]
+        p = torch.cat([rows[r][at[r]:at[r] + n[r]] for r in range(2)]).contiguous()
+        pos = _i32(list(range(at[0], at[0] + n[0])) + list(range(at[1], at[1] + n[1])))
+        starts, slots = _i32([0, n[0], n[0] + n[1]]), _i32([3, 1])
+        got = ops.retention_chunked(p, k_off, v_off, pos, inv_freq, rot, dec, dk ** -0.5, state, starts, slots, 2, max(n), H, dk, dv)
+        ref = ops.retention_scan(p, k_off, v_off, pos, inv_freq, rot, dec, dk ** -0.5, scan_state, starts, slots, 2, H, dk, dv)
+        want = torch.cat([wants[r][at[r]:at[r] + n[r]] for r in range(2)])
+        scale = max(1.0, float(want.abs().max()))
+        assert (got.double().cpu() - want).abs().max() < 5e-5 * scale, (step, float((got.double().cpu() - want).abs().max()))
+        assert (got - ref).abs().max() < 5e-5 * scale
+        at = [at[0] + n[0], at[1] + n[1]]
+    assert (state - scan_state).abs().max() < 5e-5 * max(1.0, float(scan_state.abs().max()))
+    assert float(state[0].min()) == 7.0 and float(state[2].max()) == 7.0       # the neighbours' slots are untouched
+
+
 def test_retention_keeps_a_far_write_and_forgets_by_its_decay():
     """Head 0 does not decay: what token 0 wrote is read back unchanged 600 tokens later.  Head 1 halves its state
     every token: the same read gives 2^-600, nothing."""
@@ -432,7 +472,7 @@ def test_wide_model(engines):
     100 passed in both."""
     name, T = "W", 150
     toks = U.tokens(name, T, 7)
-    got = U.run_cuts(engines(name, page_tokens=64), "a", toks, [120, 2, 5])
+    got = U.run_cuts(engines(name, page_tokens=64), "a", toks, [140, 2, 5])
     assert U.distance(got, U.plain_logits(name, T, 7)) < U.LIMIT[engines.dtype]
 
 
