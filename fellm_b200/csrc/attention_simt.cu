@@ -18,7 +18,7 @@
 // position) taken off the scaled score; a query temperature by position, q times
 // 1 + coef * ln(floor((p + 1) / every) + 1); and values that ARE the keys (vd == 0 in the record: a page-layer
 // record then holds the keys alone and the read-out has the keys' size).  kv_write puts a step's keys and values,
-// as the product left them, into their pages.
+// as the product left them, into their pages; in a decode step the attention kernel does that itself (new_k_off).
 #include "common.cuh"
 
 #define MAX_HD 256
@@ -46,8 +46,12 @@ paged_attention_simt_kernel(const TA* __restrict__ q, const TC* __restrict__ poo
                             TA* __restrict__ out, int T, int H, int G, int hd, int page_tokens, int layer,
                             int layers_in_group, float scale, int window, int vd, int ldq, float softcap, int chunk,
                             const float* __restrict__ gate, int ldg, const float* __restrict__ slopes,
-                            float qt_coef, int qt_every) {
+                            float qt_coef, int qt_every, int new_k_off, int new_v_off, int* __restrict__ status) {
   FELLM_TRACE_SCOPE(TRACE_ATTENTION_SIMT);
+  // new_k_off >= 0: a decode step, every row its request's only row.  The row's own key (and value) is read from the
+  // row itself, at columns new_k_off (new_v_off) of q's rows, and written into its page here by the first head of
+  // its kv head: no kernel in front has to write the cache, and no block reads what another writes.
+  const bool fused = new_k_off >= 0;
   extern __shared__ __align__(16) float qs[];       // [hd rounded up to 8] the query; then [nw][vd + 2] the warps' parts
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const int row = blockIdx.x / H, h = blockIdx.x - row * H;
@@ -81,8 +85,13 @@ paged_attention_simt_kernel(const TA* __restrict__ q, const TC* __restrict__ poo
       size_t tok = (size_t)g * page_tokens + (kj % page_tokens);
       const TC* krow = rec + tok * hd;
       vrow = v_is_k ? krow : rec + (size_t)G * page_tokens * hd + tok * vd;
+      const bool own = fused && kj == pos;
+      if (own) {
+        krow = (const TC*)(q + (size_t)row * ldq + new_k_off + (size_t)g * hd);
+        vrow = v_is_k ? krow : (const TC*)(q + (size_t)row * ldq + new_v_off + (size_t)g * vd);
+      }
       float dot = 0.f;
-      if (VEC) {
+      if (VEC && !own) {
         for (int e0 = 0; e0 < hd; e0 += 8) {
           float kf[8];
           load8(krow + e0, kf);
@@ -112,6 +121,22 @@ paged_attention_simt_kernel(const TA* __restrict__ q, const TC* __restrict__ poo
       for (int i = 0; i < NACC; ++i) {
         int e = lane + 32 * i;
         if (e < vd) acc[i] = fmaf(pj, to_f(vj[e]), acc[i]);
+      }
+    }
+  }
+  if (fused && h % (H / G) == 0) {
+    const int page = bt[pos / page_tokens];
+    if (page < 0) {
+      if (threadIdx.x == 0 && status) atomicExch(status, 2);
+    } else {
+      TC* rec = const_cast<TC*>(pool) + ((size_t)page * layers_in_group + layer) * record;
+      const size_t tok = (size_t)g * page_tokens + (pos % page_tokens);
+      const TA* kn = q + (size_t)row * ldq + new_k_off + (size_t)g * hd;
+      for (int e = threadIdx.x; e < hd; e += blockDim.x) rec[tok * hd + e] = from_f<TC>(to_f(kn[e]));
+      if (!v_is_k) {
+        const TA* vn = q + (size_t)row * ldq + new_v_off + (size_t)g * vd;
+        TC* vrec = rec + (size_t)G * page_tokens * hd;
+        for (int e = threadIdx.x; e < vd; e += blockDim.x) vrec[tok * vd + e] = from_f<TC>(to_f(vn[e]));
       }
     }
   }
@@ -198,7 +223,7 @@ FELLM_API int fellm_paged_attention_general(const void* q, int act_bf16, const v
                                             int page_tokens, int layer, int layers_in_group, float scale,
                                             int window, int vd, int ldq, float softcap, int chunk, const float* gate,
                                             int ldg, const float* slopes, float qt_coef, int qt_every, int warps,
-                                            cudaStream_t stream) {
+                                            int new_k_off, int new_v_off, int* status, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (hd < 1 || hd > MAX_HD || vd < 0 || vd > MAX_HD || warps < 1 || warps > 8) return FELLM_ERR_SIZE;
   if (G < 1 || H % G) return FELLM_ERR_SIZE;
@@ -211,7 +236,8 @@ FELLM_API int fellm_paged_attention_general(const void* q, int act_bf16, const v
   const bool vec = hd % 8 == 0 && ((uintptr_t)pool % 16) == 0 && (vd == 0 || vd % 8 == 0);
 #define PA(TA_, VEC_, NACC_) paged_attention_simt_kernel<TA_, TA_, VEC_, NACC_><<<blocks, warps * 32, smem, stream>>>((const TA_*)q, \
         (const TA_*)pool, block_table, max_pages, positions, row_slot, (TA_*)out, T, H, G, hd, page_tokens, \
-        layer, layers_in_group, scale, window, vd, ldq, softcap, chunk, gate, ldg, slopes, qt_coef, qt_every)
+        layer, layers_in_group, scale, window, vd, ldq, softcap, chunk, gate, ldg, slopes, qt_coef, qt_every, \
+        new_k_off, new_v_off, status)
 #define PA_N(TA_, VEC_) do { if (out_d <= 32) PA(TA_, VEC_, 1); else if (out_d <= 64) PA(TA_, VEC_, 2); \
                              else if (out_d <= 128) PA(TA_, VEC_, 4); else PA(TA_, VEC_, 8); } while (0)
   if (act_bf16) { if (vec) PA_N(bf16, true); else PA_N(bf16, false); }
@@ -228,5 +254,5 @@ FELLM_API int fellm_paged_attention_simt(const void* q, int act_bf16, const void
                                          int window, cudaStream_t stream) {
   return fellm_paged_attention_general(q, act_bf16, pool, cache_bf16, block_table, max_pages, positions, row_slot, out,
                                        T, H, G, hd, page_tokens, layer, layers_in_group, scale, window, hd, H * hd, 0.f,
-                                       0, nullptr, 0, nullptr, 0.f, 0, 1, stream);
+                                       0, nullptr, 0, nullptr, 0.f, 0, 1, -1, -1, nullptr, stream);
 }

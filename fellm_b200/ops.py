@@ -757,7 +757,8 @@ def kv_write(src, k_off, v_off, pool, block_table, positions, row_slot, layer, p
 
 
 def paged_attention_general(q, H, hd, vd, pool, block_table, positions, row_slot, layer, page_tokens, G, scale, *,
-                            window=None, chunk=None, softcap=None, gate=None, slopes=None, q_temp=None, warps=1, out=None):
+                            window=None, chunk=None, softcap=None, gate=None, slopes=None, q_temp=None, warps=1, write_new=None,
+                            out=None):
     """Attention on CUDA cores with float32 arithmetic for every form the part describes: q read in place from rows
     [T, >= H*hd] (heads at column 0), values of size vd, scores soft-capped (softcap * tanh(s / softcap)), keys limited
     to the last `window` positions and to the query's own block of `chunk` positions, and gate float32 [T, >= H]
@@ -765,6 +766,8 @@ def paged_attention_general(q, H, hd, vd, pool, block_table, positions, row_slot
     taken off the scaled score.  q_temp = (coef, every): the query at position p is multiplied by
     1 + coef ln(floor((p + 1) / every) + 1).  vd == 0: the values are the keys (a page-layer record holds keys alone).
     warps (1..8): how many warps share a (row, head)'s key tiles; a constant of the layer, since it sets the order of the sums.
+    write_new = (k_off, v_off, status): a decode step (every row its request's only one): the rows' own keys and values,
+    at those columns of q's rows, are read from there and written into their pages by this kernel (no kv_write in front).
     Returns [T, H*vd] (H*hd when the values are the keys) in q's dtype."""
     _dev(q, pool, block_table, positions, row_slot, gate, slopes)
     T = q.shape[0]
@@ -783,12 +786,14 @@ def paged_attention_general(q, H, hd, vd, pool, block_table, positions, row_slot
     qt_coef, qt_every = q_temp if q_temp else (0.0, 0)
     f = _fn("attention_simt", "fellm_paged_attention_general",
             [_c_p, _c_int, _c_p, _c_int, _c_p, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
-             _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_f, _c_int, _c_p, _c_int, _c_p, _c_f, _c_int, _c_int, _c_p])
+             _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_f, _c_int, _c_p, _c_int, _c_p, _c_f, _c_int, _c_int, _c_int,
+             _c_int, _c_p, _c_p])
+    nk, nv, status = write_new if write_new else (-1, -1, None)
     _check(f(_p(q), _is_bf16(q), _p(pool), _is_bf16(pool), _p(block_table), block_table.shape[1],
              _p(positions), _p(row_slot), _p(out), T, H, G, hd, page_tokens, layer, pool.shape[1],
              float(scale), int(window or 0), vd, q.stride(0), float(softcap or 0.0), int(chunk or 0), _p(gate),
-             gate.stride(0) if gate is not None else 0, _p(slopes), float(qt_coef), int(qt_every), int(warps), _stream()),
-           "paged_attention_general")
+             gate.stride(0) if gate is not None else 0, _p(slopes), float(qt_coef), int(qt_every), int(warps), int(nk), int(nv),
+             _p(status), _stream()), "paged_attention_general")
     return out
 
 

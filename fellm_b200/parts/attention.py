@@ -169,9 +169,18 @@ class Attention(Mixer):
         qkv = linear(xn, self.w["qkv.weight"], self.w.get("qkv.bias"))
         if self.values_are_keys:
             vd = 0              # nothing is kept beside the keys; the read-out has their size
+        if ctx.all_single:
+            # a decode step: the kernel reads each row's own key and value from the row and writes them into the page itself
+            a = ops.paged_attention_general(qkv, H, hd, vd, cache.pool, cache.block_table, ctx.positions, ctx.row_slot,
+                                            cache.layer, cache.page_tokens, G, self.scale, window=self.window,
+                                            chunk=self.chunk, softcap=self.softcap, gate=gate,
+                                            slopes=self.w.get("slopes"), q_temp=self.q_temp, warps=self.simt_warps,
+                                            write_new=(H * hd, (H + G) * hd, ctx.status))
+            linear(a, self.w["out_proj.weight"], self.w.get("out_proj.bias"), out=out, accumulate=True)
+            return out
         ops.kv_write(qkv, H * hd, (H + G) * hd, cache.pool, cache.block_table, ctx.positions, ctx.row_slot, cache.layer,
                      cache.page_tokens, G, hd, vd, status=ctx.status)
-        if self._on_tensor_cores(qkv) and not ctx.all_single:
+        if self._on_tensor_cores(qkv):
             # portions of prompts: the tensor-core kernel (keys and values of one size)
             a = ops.attention_prefill_general(qkv, H, cache.pool, cache.block_table, ctx.positions, ctx.row_slot,
                                               ctx.item_start, ctx.n_items, ctx.max_item_rows, cache.layer, self.scale,

@@ -100,9 +100,12 @@ def test_attention_at_the_edges_of_windows_and_pages(dtype, window, page, hd):
             if n <= 0:
                 break
             pos, slot = _i32(list(range(at, at + n))), _i32([r] * n)
-            ops.kv_write(qk[at:at + n], k_off, k_off, pool, table, pos, slot, 0, page, G, hd, 0)
+            if n > 1:
+                ops.kv_write(qk[at:at + n], k_off, k_off, pool, table, pos, slot, 0, page, G, hd, 0)
+            # a single row is a decode step: the kernel takes the row's own key from the row and writes the page itself
             got.append(ops.paged_attention_general(qk[at:at + n], H, hd, 0, pool, table, pos, slot, 0, page, G, 0.6,
-                                                   window=window, slopes=slopes, q_temp=(0.8, 3), warps=1 + window % 4))
+                                                   window=window, slopes=slopes, q_temp=(0.8, 3), warps=1 + window % 4,
+                                                   write_new=(k_off, k_off, None) if n == 1 else None))
             at += n
         got = torch.cat(got).double().cpu()
         tol = 1e-4 if dtype == torch.float32 else 2e-2
