@@ -96,16 +96,21 @@ __device__ __forceinline__ void attend_tile(const unsigned (&qf)[KS][4], unsigne
   }
   // scale, mask, running maximum
   float mx[2] = {m[0], m[1]};
+  // BIASED: the row's factor of the score, and the bias of the tile's key 2c for the row (the rest is slope * offset)
+  float a_row[2] = {scale_log2, scale_log2}, b_row[2] = {0.f, 0.f};
+  if (BIASED) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) { a_row[r] = scale_log2 * rs[r]; b_row[r] = -sl[r] * (float)(hi[r] - key0 - 2 * c); }
+  }
 #pragma unroll
   for (int n = 0; n < NKT; ++n) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       int key = key0 + n * 8 + 2 * c + (e & 1);
       int r = e >> 1;
-      float sc = s[n][e] * scale_log2;
-      if (BIASED) sc *= rs[r];
+      float sc = s[n][e] * (BIASED ? a_row[r] : scale_log2);
       if (CAPPED) sc = cap_log2 * tanhf(sc / cap_log2);
-      if (BIASED) sc -= sl[r] * (float)(hi[r] - key);
+      if (BIASED) sc += fmaf(sl[r], (float)(n * 8 + (e & 1)), b_row[r]);       // - slope * (hi - key)
       float v = (!MASKED || (key >= lo[r] && key <= hi[r])) ? sc : -INFINITY;
       s[n][e] = v;
       mx[r] = fmaxf(mx[r], v);
@@ -389,7 +394,10 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(AttnAr
       int warp_hi = pos0 + min(n_tok - 1, (warp * 16 + 15) / R);
       if (key0 <= warp_hi && warp * 16 < n_tok * R) {
         if (biased) {
+          // a tile that every row of the warp sees whole (behind the window's lower edge, in front of the diagonal) needs no mask
+          const bool whole = key0 >= max(lo[0], lo[1]) && key0 + PF_TK - 1 <= min(hi[0], hi[1]);
           if (a.cap_log2 > 0.f) attend_tile<PF_TK / 8, true, true, true>(qf, ks, vs, key0, lo, hi, a.scale_log2, o, m, l, lane, a.cap_log2, rs, sl);
+          else if (__all_sync(0xffffffffu, whole)) attend_tile<PF_TK / 8, false, false, true>(qf, ks, vs, key0, lo, hi, a.scale_log2, o, m, l, lane, 0.f, rs, sl);
           else attend_tile<PF_TK / 8, true, false, true>(qf, ks, vs, key0, lo, hi, a.scale_log2, o, m, l, lane, 0.f, rs, sl);
         } else if (a.cap_log2 > 0.f) attend_tile<PF_TK / 8, true, true>(qf, ks, vs, key0, lo, hi, a.scale_log2, o, m, l, lane, a.cap_log2);
         else attend_tile<PF_TK / 8>(qf, ks, vs, key0, lo, hi, a.scale_log2, o, m, l, lane);
