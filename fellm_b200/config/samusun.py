@@ -27,22 +27,25 @@ class WindowAttentionConfig:
     dim: int
     vdim: int
     scale: float
-    window: int
+    window: Optional[int]
     q_temp_coef: float
     q_temp_every: int
 
     @staticmethod
     def read(d, where):
-        mask = _get(d, "mask", dict, where)
-        qt = _get(d, "q_temp", dict, where)
-        c = WindowAttentionConfig(heads=_get(d, "heads", int, where, positive=True),
-                                  kv_heads=_get(d, "kv_heads", int, where, positive=True),
-                                  dim=_get(d, "dim", int, where, positive=True),
-                                  vdim=_get(d, "vdim", int, where, positive=True),
+        # a file that leaves out the window or the temperature has none; kv_heads defaults to heads
+        mask = _get(d, "mask", dict, where, required=False)
+        qt = _get(d, "q_temp", dict, where, required=False)
+        heads = _get(d, "heads", int, where, positive=True)
+        dim = _get(d, "dim", int, where, positive=True)
+        c = WindowAttentionConfig(heads=heads,
+                                  kv_heads=_get(d, "kv_heads", int, where, positive=True, required=False, default=heads),
+                                  dim=dim,
+                                  vdim=_get(d, "vdim", int, where, positive=True, required=False, default=dim),
                                   scale=_get(d, "scale", float, where),
-                                  window=_get(mask, "size", int, where + ".mask", positive=True),
-                                  q_temp_coef=_get(qt, "coef", float, where + ".q_temp"),
-                                  q_temp_every=_get(qt, "every", int, where + ".q_temp", positive=True))
+                                  window=None if mask is None else _get(mask, "size", int, where + ".mask", positive=True),
+                                  q_temp_coef=0.0 if qt is None else _get(qt, "coef", float, where + ".q_temp"),
+                                  q_temp_every=0 if qt is None else _get(qt, "every", int, where + ".q_temp", positive=True))
         if c.heads % c.kv_heads:
             raise ConfigError(f"config.json: '{where}.heads' ({c.heads}) is not a multiple of kv_heads ({c.kv_heads})")
         if c.vdim != c.dim:
@@ -50,8 +53,12 @@ class WindowAttentionConfig:
         return c
 
     def to_dict(self):
-        return dict(dim=self.dim, heads=self.heads, kv_heads=self.kv_heads, mask=dict(size=self.window),
-                    q_temp=dict(coef=self.q_temp_coef, every=self.q_temp_every), scale=self.scale, vdim=self.vdim)
+        d = dict(dim=self.dim, heads=self.heads, kv_heads=self.kv_heads, scale=self.scale, vdim=self.vdim)
+        if self.window is not None:
+            d["mask"] = dict(size=self.window)
+        if self.q_temp_every:
+            d["q_temp"] = dict(coef=self.q_temp_coef, every=self.q_temp_every)
+        return d
 
 
 @dataclass(frozen=True)
@@ -66,7 +73,7 @@ class RetentionConfig:
 
     @staticmethod
     def read(d, where):
-        rot = _get(d, "rot", dict, where)
+        rot = _get(d, "rot", dict, where, required=False)          # left out: no rotation
         decay = d.get("decay")
         if not isinstance(decay, list) or any(isinstance(g, bool) or not isinstance(g, (int, float)) for g in decay):
             raise ConfigError(f"config.json: '{where}.decay' must be a list of numbers")
@@ -74,8 +81,8 @@ class RetentionConfig:
                             dim=_get(d, "dim", int, where, positive=True),
                             vdim=_get(d, "vdim", int, where, positive=True),
                             decay=tuple(float(g) for g in decay),
-                            rot_dims=_get(rot, "dims", int, where + ".rot"),
-                            rot_base=_get(rot, "base", float, where + ".rot"))
+                            rot_dims=0 if rot is None else _get(rot, "dims", int, where + ".rot"),
+                            rot_base=10000.0 if rot is None else _get(rot, "base", float, where + ".rot"))
         if len(c.decay) != c.heads:
             raise ConfigError(f"config.json: '{where}.decay' has {len(c.decay)} entries for {c.heads} heads")
         if c.rot_dims % 2 or not 0 <= c.rot_dims <= c.dim:

@@ -35,7 +35,8 @@ def _attention(p: str, d: int, m, eps: float) -> PartSpec:
              "out_proj.weight": p + "o", "out_proj.bias": p + "o.b"}
     return PartSpec.make("attention", names=names, size=d, heads=m.heads, kv_heads=m.kv_heads, head_dim=m.dim,
                          qk_norm=False, norm_eps=eps, position=PartSpec.make("none"), window=m.window, scale=m.scale,
-                         bias=True, values_are_keys=True, slope_exp=SLOPE_EXP, q_temp=(m.q_temp_coef, m.q_temp_every))
+                         bias=True, values_are_keys=True, slope_exp=SLOPE_EXP,
+                         q_temp=(m.q_temp_coef, m.q_temp_every) if m.q_temp_every else None)
 
 
 def _retention(p: str, d: int, m, eps: float) -> PartSpec:
