@@ -258,11 +258,13 @@ def test_retention_keeps_a_far_write_and_forgets_by_its_decay():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T,d,ff,E,top", [(1, 64, 24, 4, 2), (3, 96, 40, 5, 1), (70, 72, 9, 7, 3), (700, 128, 56, 6, 6), (1300, 64, 32, 8, 2)])
+@pytest.mark.parametrize("T,d,ff,E,top", [(1, 64, 24, 4, 2), (3, 96, 40, 5, 1), (70, 72, 9, 7, 3), (700, 128, 56, 6, 6), (1300, 64, 32, 8, 2),
+                                          (300, 64, 24, 1, 1), (400, 72, 16, 2, 2)])
 def test_routed_experts_from_logits_to_the_weighted_sum(dtype, T, d, ff, E, top):
     """Routing, the device-side plan, both grouped products and the combine against the plain mixture.  Expert e's
     down projection is scaled by 3^e: a row sent to the wrong expert, or weighted by the wrong score, is far off.
-    1,300 tokens x 2 choices are more pairs than one tile of the plan holds."""
+    1,300 tokens x 2 choices are more pairs than one tile of the plan holds; one or two small experts are fewer weight rows
+    than a tile of the tensor-core product has."""
     from fellm_b200 import ops
     g = torch.Generator().manual_seed(T + E)
     W = {"router": (torch.randn(E, d, generator=g) * 0.5).bfloat16().double()}
